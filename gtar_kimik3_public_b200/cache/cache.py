@@ -11,7 +11,8 @@ fixed size per batch row (src/cache.py:48-57).  Here
   live sequences hold (each rounded up to a page) and not by slots times the longest context;
 * layers whose mixers ask for the same kind of storage form a *group* with tensors and a page
   pool of its own: one group for "all positions", one per window length (pages that have left
-  the window go back to the pool), one per shape of fixed-size state;
+  the window go back to the pool), one per shape of fixed-size state; a group's pages hold keys and
+  values per kv head, or one row per position for all heads (a layer that attends through a latent);
 * stale data is never cleared from pages: nothing reads beyond a sequence's length (the
   reference argues the same for its rollback, src/cache.py:37-45).  State rows are zeroed when
   a slot is handed out.
@@ -26,8 +27,8 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..ops.functional import DecodeWork, PagedKV
-from ..parts.base import KVRequest, StateRequest
+from ..ops.functional import DecodeWork, PagedKV, PagedRows
+from ..parts.base import KVRequest, RowsRequest, StateRequest
 from .allocators import CacheFull, PageAllocator, SlotAllocator
 
 PAGE_SIZE = 64
@@ -57,15 +58,19 @@ class CacheLayout:
 
 
 class _KVGroup:
-    def __init__(self, request: KVRequest, items: list[tuple[int, int]], n_slots: int, n_pages: int, max_pages_per_seq: int,
+    def __init__(self, request: KVRequest | RowsRequest, items: list[tuple[int, int]], n_slots: int, n_pages: int, max_pages_per_seq: int,
                  page_size: int, dtype: torch.dtype, device: torch.device):
         # items: (run-list entry, place among that entry's requests) of everything stored here
         self.request, self.items, self.page_size = request, items, page_size
         self.entries = [entry for entry, _ in items]
         self.index_of = {item: i for i, item in enumerate(items)}
-        shape = (len(items), n_pages, request.n_kv_heads, page_size, request.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        if isinstance(request, RowsRequest):  # one row per position; no second tensor
+            self.k = torch.empty((len(items), n_pages, page_size, request.width), dtype=dtype, device=device)
+            self.v = None
+        else:
+            shape = (len(items), n_pages, request.n_kv_heads, page_size, request.head_dim)
+            self.k = torch.empty(shape, dtype=dtype, device=device)
+            self.v = torch.empty(shape, dtype=dtype, device=device)
         self.pages = PageAllocator(n_pages)
         self.max_pages_per_seq = max_pages_per_seq
         self.table_host = np.zeros((n_slots, max_pages_per_seq), dtype=np.int32)
@@ -150,8 +155,10 @@ class _KVGroup:
         self._staging_events[turn] = event
         self.dirty.clear()
 
-    def view(self, item: tuple[int, int]) -> PagedKV:
+    def view(self, item: tuple[int, int]) -> PagedKV | PagedRows:
         i = self.index_of[item]
+        if self.v is None:
+            return PagedRows(self.k[i], self.table)
         if self._work is None and self.table.is_cuda:
             self._work = DecodeWork(self.table.device)
         return PagedKV(self.k[i], self.v[i], self.table, self._work)
@@ -199,7 +206,7 @@ class Cache:
             for place, request in enumerate(layout.items_of(entry)):
                 by_request.setdefault(request, []).append((entry, place))
         for request, entries in by_request.items():
-            if isinstance(request, KVRequest):
+            if isinstance(request, (KVRequest, RowsRequest)):
                 # A windowed group draws on a pool as large as the others': a long prompt needs all its
                 # pages while its step runs.  What the window saves is returned at the sequence's
                 # next step, so fewer pages are *in use*, and more sequences fit, than without it.
@@ -284,7 +291,10 @@ class Cache:
         total = 0
         for group in self.kv_groups:
             r = group.request
-            total += 2 * len(group.items) * r.n_kv_heads * r.head_dim * self.k_element_size()
+            if isinstance(r, RowsRequest):
+                total += len(group.items) * r.width * self.k_element_size()
+            else:
+                total += 2 * len(group.items) * r.n_kv_heads * r.head_dim * self.k_element_size()
         return total
 
     def k_element_size(self) -> int:

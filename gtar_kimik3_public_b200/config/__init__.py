@@ -2,3 +2,4 @@
 
 from .base import ConfigError, ModelConfig, architecture_name, read_config_json  # noqa: F401
 from .transformer import TransformerConfig  # noqa: F401
+from .dasusun import DasusunConfig  # noqa: F401

@@ -141,10 +141,11 @@ def read_config_json(path: str | Path) -> dict[str, Any]:
 
 
 def architecture_name(raw: dict[str, Any]) -> str:
-    """The architecture string of a config dict: ``arch`` or the first of ``architectures``."""
-    if isinstance(raw.get("arch"), str):
-        return raw["arch"]
+    """The architecture string of a config dict: ``arch``, ``architecture`` or the first of ``architectures``."""
+    for key in ("arch", "architecture"):
+        if isinstance(raw.get(key), str):
+            return raw[key]
     names = raw.get("architectures")
     if isinstance(names, (list, tuple)) and names and isinstance(names[0], str):
         return names[0]
-    raise ConfigError('config has neither "arch" nor "architectures"; cannot choose a model class')
+    raise ConfigError('config has neither "arch", "architecture" nor "architectures"; cannot choose a model class')

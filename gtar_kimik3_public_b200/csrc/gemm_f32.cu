@@ -17,11 +17,15 @@ constexpr int BM = 128, BN = 128, BK = 8, TM = 8, TN = 8, THREADS = 256;
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(THREADS) gemm_f32_kernel(const TA* __restrict__ A, const float* __restrict__ W,
                                                            TC* __restrict__ C, int M, int N, int K, long long lda,
-                                                           long long ldw, long long ldc) {
+                                                           long long ldw, long long ldc, long long batch_a,
+                                                           long long batch_w, long long batch_c) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     pdl_launch_dependents();
     pdl_wait();
+    A += (size_t)blockIdx.z * batch_a;  // a batch of products: one per grid plane, each with the chains of a single one
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = tid / (BN / TN), tx = tid % (BN / TN);
@@ -87,9 +91,32 @@ GK_EXPORT int gk_gemm_f32(const void* A, int a_dtype, const float* W, void* C, i
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(a_dtype, TA, {
         GK_DISPATCH_DTYPE(c_dtype, TC, {
-            gk_launch(gemm_f32_kernel<TA, TC>, grid, dim3(THREADS), 0, s, (const TA*)A, W, (TC*)C, M, N, K, lda, ldw, ldc);
+            gk_launch(gemm_f32_kernel<TA, TC>, grid, dim3(THREADS), 0, s, (const TA*)A, W, (TC*)C, M, N, K, lda, ldw, ldc, 0LL, 0LL, 0LL);
         })
     })
     GK_CHECK_LAUNCH("gemm_f32");
+    return GK_OK;
+}
+
+// `batch` products at once: product b reads A + b * batch_a and W + b * batch_w and writes C + b * batch_c (strides in
+// elements).  Rows may be strided (lda, ldw, ldc), so heads that lie side by side in a row are products of one batch.
+GK_EXPORT int gk_gemm_f32_batched(const void* A, int a_dtype, const float* W, void* C, int c_dtype, int batch, int M, int N,
+                                  int K, long long lda, long long ldw, long long ldc, long long batch_a, long long batch_w,
+                                  long long batch_c, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(a_dtype) && GK_VALID_DTYPE(c_dtype), "gemm_f32_batched: bad dtype code");
+    GK_REQUIRE(batch > 0 && batch <= 65535 && M >= 0 && N > 0 && K > 0, "gemm_f32_batched: bad sizes batch=%d M=%d N=%d K=%d",
+               batch, M, N, K);
+    GK_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_f32_batched: a leading dimension is shorter than its row");
+    if (M == 0) return GK_OK;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    GK_REQUIRE(grid.y <= 65535u, "gemm_f32_batched: M=%d needs more than 65535 row tiles", M);
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(a_dtype, TA, {
+        GK_DISPATCH_DTYPE(c_dtype, TC, {
+            gk_launch(gemm_f32_kernel<TA, TC>, grid, dim3(THREADS), 0, s, (const TA*)A, W, (TC*)C, M, N, K, lda, ldw, ldc,
+                      batch_a, batch_w, batch_c);
+        })
+    })
+    GK_CHECK_LAUNCH("gemm_f32_batched");
     return GK_OK;
 }

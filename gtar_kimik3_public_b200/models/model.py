@@ -39,6 +39,9 @@ class ModelPlan:
     layer_prefix: str = "model.layers.{}."
     final_norm_prefix: str = "model.norm."
     head_prefix: str = "lm_head."
+    # Layers that mix the results of earlier layers into their stream need those kept for the length of a step:
+    # how many streams a step keeps (the embedding output and every layer's result), 0 for none.
+    keep_streams: int = 0
 
 
 class Model:
@@ -78,7 +81,7 @@ class Model:
     # ------------------------------------------------------------------ cache
     def cache_layout(self) -> CacheLayout:
         plan = self.plan
-        requests = [plan.layers[e.layer].mixer.cache_request() for e in plan.run_list]
+        requests = [plan.layers[e.layer].cache_request() for e in plan.run_list]
         shared = {i: e.cache_of for i, e in enumerate(plan.run_list) if e.cache_of is not None}
         return CacheLayout(requests, shared)
 
@@ -116,7 +119,13 @@ class Model:
         at ``ctx.want_rows``."""
         plan = self.plan
         self.prepare(ctx.max_position)
-        h = plan.embedding.forward(ctx.tokens)
+        if plan.keep_streams:
+            # entry 0 is the embedding output; a block writes its own result into the entry after its place
+            kept = torch.empty((plan.keep_streams, ctx.n_tokens, plan.embedding.hidden_size), dtype=torch.float32, device=self.device)
+            h = plan.embedding.forward(ctx.tokens, out=kept[0])
+            ctx.extras["kept_streams"] = kept
+        else:
+            h = plan.embedding.forward(ctx.tokens)
         pending = None
         persistent = self.persistent_decode(cache) if ctx.all_single and ctx.n_seqs <= F.DECODE_LAYERS_MAX_SEQS else None
         if persistent is not None:

@@ -62,3 +62,15 @@ def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: i
     if fast:
         return F.attention_prefill(q, kv, ctx.cu_q, ctx.kv_len, ctx.slots, ctx.max_q_len, scale, window)
     return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window)
+
+
+def latent_attention(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_at: int, rot: int, rot_dims: int, cos, sin,
+                     cache: F.PagedRows, ctx, scale: float, window: int, out: torch.Tensor) -> torch.Tensor:
+    """Attention of the step's queries over each sequence's cached latent rows (the new tokens' own are already
+    written): ``q_carried [n_tokens, n_heads, rank]`` is the unrotated query carried into the latent, ``q_raw`` holds
+    each head's own part to rotate at ``q_rot_at``; ``out [n_tokens, n_heads, rank]`` is the weighted sum of latents."""
+    if q_raw.dtype == torch.bfloat16 and F.latent_tiled_ok(q_carried.shape[1], q_carried.shape[2], rot, cache):
+        return F.attention_latent_tiled(q_carried, q_raw, q_rot_at, rot, rot_dims, cos, sin, cache, ctx.tok_pos, ctx.tok_seq,
+                                        ctx.cu_q, ctx.slots, scale, window, out, ctx.max_q_len)
+    return F.attention_latent_exact(q_carried, q_raw, q_rot_at, rot, rot_dims, cos, sin, cache, ctx.tok_pos, ctx.tok_seq,
+                                    ctx.slots, scale, window, out)

@@ -1016,3 +1016,176 @@ def decode_layers(layer_table: torch.Tensor, n_layers: int, h: torch.Tensor, n_q
          ptr(act), ptr(part), part.numel(), ptr(words), ptr(kv_len), ptr(slots), ptr(block_table), block_table.shape[1],
          int(max_kv_len), ptr(cos), ptr(sin), table_positions, int(norm_bf16), int(qk_bf16), float(scale),
          ptr(error_flag(h.device)), ptr(stamps), stream_ptr())
+
+
+# ------------------------------------------------------------------ rows in pages, and attention through a latent
+@dataclass
+class PagedRows:
+    """One layer's per-position rows in pages: ``rows [n_pages, page_size, width]`` and the table that maps a
+    sequence's pages (as in ``PagedKV``).  A latent-attention layer keeps one such row per position for all heads."""
+
+    rows: torch.Tensor
+    block_table: torch.Tensor
+
+    @property
+    def page_size(self) -> int:
+        return self.rows.shape[1]
+
+    @property
+    def max_pages(self) -> int:
+        return self.block_table.shape[1]
+
+
+def branch_merge(x: torch.Tensor, y: torch.Tensor, norm_weight: torch.Tensor, eps: float, scale: torch.Tensor | None = None,
+                 kept: torch.Tensor | None = None, n_kept: int = 0, mix: torch.Tensor | None = None,
+                 next_weight: torch.Tensor | None = None, next_eps: float = 0.0, next_dtype: torch.dtype = torch.float32,
+                 x_out: torch.Tensor | None = None):
+    """``v = x + scale * rmsnorm(y) * norm_weight``; with ``kept`` ``[n, rows, width]``: ``kept[n_kept] = v`` and
+    ``v = sum_{j <= n_kept} mix[j] * kept[j]``; the new stream goes to ``x_out`` (default: ``x`` itself); with
+    ``next_weight`` also returns ``rmsnorm(v) * next_weight`` in ``next_dtype``.  All weights are 32-bit effective
+    weights.  Returns ``(stream, normed or None)``."""
+    require_device(x.device)
+    _check(x, "x", torch.float32, 2)
+    _check(y, "y", dims=2)
+    rows, width = x.shape
+    if y.shape != x.shape:
+        raise KernelError(f"branch {tuple(y.shape)} does not match the stream {tuple(x.shape)}")
+    for name, t in (("norm_weight", norm_weight), ("scale", scale), ("next_weight", next_weight)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != width:
+                raise KernelError(f"{name} has {t.shape[0]} entries for rows of {width}")
+    stride = 0
+    if kept is not None:
+        _check(kept, "kept", torch.float32, 3)
+        _check(mix, "mix", torch.float32, 1)
+        if kept.shape[1:] != x.shape or not 0 <= n_kept < kept.shape[0] or mix.shape[0] != n_kept + 1:
+            raise KernelError(f"history {tuple(kept.shape)} / mixing weights {tuple(mix.shape)} do not fit entry {n_kept} of a "
+                              f"stream {tuple(x.shape)}")
+        stride = kept.stride(0)
+    if x_out is None:
+        x_out = x
+    _check(x_out, "x_out", torch.float32, 2)
+    z = None
+    if next_weight is not None:
+        z = torch.empty((rows, width), dtype=next_dtype, device=x.device)
+    call("gk_branch_merge", ptr(x), ptr(y), dtype_code(y.dtype), ptr(norm_weight), ptr(scale), float(eps), ptr(kept), stride,
+         int(n_kept), ptr(mix), ptr(x_out), ptr(next_weight), float(next_eps), ptr(z), dtype_code(next_dtype), rows, width,
+         stream_ptr())
+    return x_out, z
+
+
+def causal_conv(a: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                cu_q: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``a + conv(a)`` over time on each channel: ``a [n_tokens, width]`` 32-bit, ``weight [width, taps]`` 32-bit,
+    ``state [n_slots, taps - 1, width]`` the sequences' inputs of before (read only; see ``conv_state``)."""
+    require_device(a.device)
+    _check(a, "a", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 2)
+    n, width = a.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != width:
+        raise KernelError(f"convolution weights {tuple(weight.shape)} for rows of {width}")
+    if taps > 1:
+        _check(state, "state", torch.float32, 3)
+        if tuple(state.shape[1:]) != (taps - 1, width):
+            raise KernelError(f"state {tuple(state.shape)} does not hold {taps - 1} inputs of width {width}")
+    out = torch.empty((n, width), dtype=out_dtype, device=a.device)
+    call("gk_causal_conv", ptr(a), ptr(weight), ptr(state) if taps > 1 else None, ptr(tok_pos), ptr(tok_seq), ptr(cu_q),
+         ptr(slots), ptr(out), dtype_code(out_dtype), n, width, taps, stream_ptr())
+    return out
+
+
+def conv_state(a: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slots: torch.Tensor, n_seqs: int) -> None:
+    """Brings the sequences' convolution states up to date after ``causal_conv`` has read them: each holds its
+    sequence's last ``taps - 1`` inputs."""
+    _check(a, "a", torch.float32, 2)
+    _check(state, "state", torch.float32, 3)
+    call("gk_conv_state", ptr(a), ptr(state), ptr(cu_q), ptr(slots), int(n_seqs), a.shape[1], state.shape[1] + 1, stream_ptr())
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    """``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))`` in 32-bit, element by element."""
+    require_device(x.device)
+    _check(x, "x")
+    out = torch.empty_like(x)
+    call("gk_gelu_tanh", ptr(x), ptr(out), dtype_code(x.dtype), x.numel(), stream_ptr())
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, rank: int, rot: int, rot_dims: int, w_q: torch.Tensor, w_kv: torch.Tensor,
+                   eps: float, cos: torch.Tensor | None, sin: torch.Tensor | None, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                   slots: torch.Tensor, cache: PagedRows, max_position: int, write: bool = True) -> torch.Tensor:
+    """From the packed projection rows ``[q latent | kv latent | shared key part]``: returns the normed q latent
+    ``[n, q_rank]`` and writes each position's cache row (normed kv latent, rotated shared key part)."""
+    require_device(proj.device)
+    _check(proj, "proj", dims=2)
+    n = proj.shape[0]
+    if proj.shape[1] != q_rank + rank + rot:
+        raise KernelError(f"projection rows of {proj.shape[1]} are not {q_rank} + {rank} + {rot}")
+    _check(w_q, "w_q", torch.float32, 1)
+    _check(w_kv, "w_kv", torch.float32, 1)
+    _check(cache.rows, "cache rows", proj.dtype, 3)
+    if cache.rows.shape[2] != rank + rot:
+        raise KernelError(f"cache rows of {cache.rows.shape[2]} are not {rank} + {rot}")
+    table_rows = 0
+    if rot_dims:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
+            raise KernelError(f"rotation tables {tuple(cos.shape)} do not hold {rot_dims // 2} angles a position")
+        table_rows = cos.shape[0]
+    out = torch.empty((n, q_rank), dtype=proj.dtype, device=proj.device)
+    call("gk_latent_prepare", ptr(proj), dtype_code(proj.dtype), ptr(w_q), ptr(w_kv), float(eps), ptr(cos), ptr(sin),
+         ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(cache.block_table), ptr(out), ptr(cache.rows) if write else None, n, q_rank,
+         rank, rot, rot_dims, cache.max_pages, cache.page_size, int(max_position), table_rows, stream_ptr())
+    return out
+
+
+def attention_latent_exact(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_at: int, rot: int, rot_dims: int,
+                           cos: torch.Tensor | None, sin: torch.Tensor | None, cache: PagedRows, tok_pos: torch.Tensor,
+                           tok_seq: torch.Tensor, slots: torch.Tensor, scale: float, window: int, out: torch.Tensor) -> torch.Tensor:
+    """Attention of ``[q_carried (rank) | rotated part of q_raw]`` over the cached rows; the value of a row is its
+    first ``rank`` entries.  ``q_carried`` and ``out`` are ``[n_tokens, n_heads, rank]`` views with any token and
+    head strides (innermost contiguous); ``q_raw [n_tokens, n_heads, d]`` holds each head's part to rotate at
+    ``q_rot_at``."""
+    require_device(q_raw.device)
+    _check(q_raw, "q_raw", dims=3)
+    n, heads, raw_dim = q_raw.shape
+    rank = q_carried.shape[2]
+    for name, t in (("q_carried", q_carried), ("out", out)):
+        if t.dtype != q_raw.dtype or tuple(t.shape) != (n, heads, rank) or t.stride(2) != 1:
+            raise KernelError(f"{name} must be {q_raw.dtype} [{n}, {heads}, {rank}] with a contiguous last axis")
+    _check(cache.rows, "cache rows", q_raw.dtype, 3)
+    if cache.rows.shape[2] != rank + rot:
+        raise KernelError(f"cache rows of {cache.rows.shape[2]} are not {rank} + {rot}")
+    call("gk_attention_latent_exact", ptr(q_carried), q_carried.stride(0), q_carried.stride(1), ptr(q_raw), raw_dim, int(q_rot_at),
+         ptr(cos), ptr(sin), ptr(cache.rows), ptr(out), out.stride(0), out.stride(1), dtype_code(q_raw.dtype), ptr(tok_pos),
+         ptr(tok_seq), ptr(slots), ptr(cache.block_table), n, heads, rank, rot, rot_dims, cache.max_pages, cache.page_size,
+         float(scale), int(window), stream_ptr())
+    return out
+
+
+def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[b] = x[b] @ weight[b].T`` for a batch of products (one per head): ``x [B, M, K]`` and ``out [B, M, N]`` may be
+    views with any batch and row strides (innermost contiguous), ``weight [B, N, K]`` is contiguous.  float32 weights go
+    through the FP32-pipe kernel, bfloat16 ones through the library's batched product with 32-bit accumulation."""
+    require_device(x.device)
+    b, m, k = x.shape
+    n = weight.shape[1]
+    _check(weight, "weight", dims=3)
+    if weight.shape[0] != b or weight.shape[2] != k or tuple(out.shape) != (b, m, n) or x.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError(f"batched product of {tuple(x.shape)} with {tuple(weight.shape)} into {tuple(out.shape)}")
+    if weight.dtype == torch.float32:
+        call("gk_gemm_f32_batched", ptr(x), dtype_code(x.dtype), ptr(weight), ptr(out), dtype_code(out.dtype), b, m, n, k,
+             x.stride(1), k, out.stride(1), x.stride(0), n * k, out.stride(0), stream_ptr())
+        return out
+    if weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("a bfloat16 batched product needs bfloat16 operands and output")
+    torch.bmm(x, weight.transpose(1, 2), out=out)
+    return out
+
+
+def latent_tiled_ok(n_heads: int, rank: int, rot: int, cache: PagedRows) -> bool:
+    """Whether the tensor-core kernel takes the layer (none is built for these rows yet: the exact kernel runs)."""
+    return False

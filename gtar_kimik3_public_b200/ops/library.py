@@ -36,6 +36,13 @@ _SIGNATURES: dict[str, list] = {
     "gk_decode_layers": [P, I, I, I, I, I, I, I, P, P, P, P, P, L, P, P, P, P, I, I, P, P, I, I, I, F, P, P, P],
     "gk_qk_norm_rope_write": [P, I, P, P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_f32": [P, I, P, P, I, I, I, I, L, L, L, P],
+    "gk_gemm_f32_batched": [P, I, P, P, I, I, I, I, I, L, L, L, L, L, L, P],
+    "gk_branch_merge": [P, P, I, P, P, F, P, L, I, P, P, P, F, P, I, I, I, P],
+    "gk_causal_conv": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "gk_conv_state": [P, P, P, P, I, I, I, P],
+    "gk_gelu_tanh": [P, P, I, L, P],
+    "gk_latent_prepare": [P, I, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+    "gk_attention_latent_exact": [P, L, L, P, I, I, P, P, P, P, L, L, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, I, I, P, P],

@@ -35,6 +35,8 @@ class TensorSpec:
     shape: tuple[int, ...]
     kind: str = "matrix"
     optional: bool = False
+    # (mean, standard deviation) that the random-weights mode draws the tensor with; None: the mode's rule for the kind
+    init: tuple[float, float] | None = None
 
 
 @dataclass(frozen=True)
@@ -43,6 +45,15 @@ class KVRequest:
 
     n_kv_heads: int
     head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class RowsRequest:
+    """One row of ``width`` numbers per position, in pages (what a layer that attends through a latent keeps:
+    the latent and a shared key part, for all heads).  ``window`` = None keeps all positions."""
+
+    width: int
     window: int | None = None
 
 
@@ -139,6 +150,11 @@ class FeedForward(Part):
 
 class Block(Part):
     """Arrangement of the parts of one layer around the residual stream."""
+
+    def cache_request(self):
+        """What the layer needs kept between steps: its mixer's request, unless the arrangement itself keeps
+        something too (it then returns a list, and ``forward`` gets a tuple of views in the list's order)."""
+        return self.mixer.cache_request()
 
     def children(self) -> list[tuple[str, Part]]:
         """(tensor-name prefix, part) of everything inside the block."""

@@ -4,6 +4,9 @@ block hands its last branch output on as ``pending`` instead of adding it itself
 
 from __future__ import annotations
 
+import torch
+
+from ..ops import functional as F
 from .base import Block, FeedForward, Mixer, Norm, StepContext, register_part
 
 
@@ -83,3 +86,132 @@ class PreNormBlock(Block):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class SandwichBlock(Block):
+    """A layer that norms every branch before AND after it, scales it per channel, passes the mixer's input
+    through a short causal convolution over time, and mixes the results of all earlier layers into what it hands on:
+
+        a = norm_in(x);  a += conv(a)                      (conv: ``taps`` taps per channel, zeros before the start)
+        x += scale_1 * norm_out_1(mixer(a))
+        x += scale_2 * norm_out_2(feed_forward(norm_mid(x)))          (left out for a layer without feed-forward)
+        X_(i+1) = x;   handed on: sum_{j <= i+1} mix[j] * X_j         (X_0 the embedding output, i this layer's place)
+
+    The last ``taps - 1`` inputs of the convolution are part of a sequence's state.  Every sum into the stream, the
+    norm of the branch before it, the depth mix and the norm that reads the result are one kernel (``branch_merge``);
+    the norm at the head of the NEXT layer is formed there too when the next layer is of this kind (``next_block``).
+    The step keeps the streams ``X_j`` (``ctx.extras["kept_streams"]``, made by the model).
+    """
+
+    def __init__(self, width: int, place: int, norm_in: Norm, mixer: Mixer, norm_out_1: Norm, norm_mid: Norm | None,
+                 feed_forward: FeedForward | None, norm_out_2: Norm | None, conv_taps: int = 0,
+                 names: dict[str, str] | None = None):
+        self.width, self.place, self.conv_taps = int(width), int(place), int(conv_taps)
+        self.norm_in, self.mixer, self.norm_out_1 = norm_in, mixer, norm_out_1
+        self.norm_mid, self.feed_forward, self.norm_out_2 = norm_mid, feed_forward, norm_out_2
+        if (feed_forward is None) != (norm_mid is None) or (feed_forward is None) != (norm_out_2 is None):
+            raise ValueError("a feed-forward comes with the norms before and after it, or not at all")
+        self.names = {"mixer": "mix.", "feed_forward": "mlp.", "scale_1": "ls1", "scale_2": "ls2", "conv": "canon1",
+                      "mix": "dwa", **(names or {})}
+        self.next_block: SandwichBlock | None = None
+        self.scale_1 = self.scale_2 = self.conv = self.mix = None
+
+    def children(self):
+        parts = [("", self.norm_in), (self.names["mixer"], self.mixer), ("", self.norm_out_1)]
+        if self.feed_forward is not None:
+            parts += [("", self.norm_mid), (self.names["feed_forward"], self.feed_forward), ("", self.norm_out_2)]
+        return parts
+
+    def _own_specs(self):
+        from .base import TensorSpec
+
+        specs = {self.names["scale_1"]: TensorSpec((self.width,), "vector", init=(1.0, 0.2)),
+                 self.names["mix"]: TensorSpec((self.place + 2,), "vector", init=(0.4, 0.3))}
+        if self.feed_forward is not None:
+            specs[self.names["scale_2"]] = TensorSpec((self.width,), "vector", init=(1.0, 0.2))
+        if self.conv_taps:
+            specs[self.names["conv"]] = TensorSpec((self.width, self.conv_taps), "matrix", init=(0.0, 0.3))
+        return specs
+
+    def tensor_specs(self):
+        specs = {prefix + name: spec for prefix, part in self.children() for name, spec in part.tensor_specs().items()}
+        specs.update(self._own_specs())
+        return specs
+
+    def load(self, tensors):
+        for prefix, part in self.children():
+            part.load({name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors})
+        for _, part in self.children():
+            if isinstance(part, Norm) and getattr(part, "weight", None) is not None:
+                part.weight = part.weight.float().contiguous()  # the merging kernel multiplies by 32-bit weights
+        n = self.names
+        self.scale_1 = tensors[n["scale_1"]].float().contiguous()
+        self.mix = tensors[n["mix"]].float().contiguous()
+        if self.feed_forward is not None:
+            self.scale_2 = tensors[n["scale_2"]].float().contiguous()
+        if self.conv_taps:
+            self.conv = tensors[n["conv"]].float().contiguous()
+
+    def weight_bytes(self):
+        own = sum(t.numel() * t.element_size() for t in (self.scale_1, self.scale_2, self.conv, self.mix) if t is not None)
+        return own + sum(part.weight_bytes() for _, part in self.children())
+
+    def cache_request(self):
+        request = self.mixer.cache_request()
+        if self.conv_taps <= 1:
+            return request
+        from .base import StateRequest
+
+        own = StateRequest((self.conv_taps - 1, self.width), torch.float32)
+        if request is None:
+            return [own]
+        return [*request, own] if isinstance(request, (list, tuple)) else [request, own]
+
+    def input_dtype(self, ctx: StepContext) -> torch.dtype:
+        """What the norm at the head of the layer is wanted in: 32-bit where the convolution reads it."""
+        return torch.float32 if self.conv_taps else ctx.dtype
+
+    def forward(self, h, pending, ctx: StepContext, cache):
+        if pending is not None:
+            raise ValueError("a layer of this kind takes its stream whole: the layer before must not leave a branch unadded")
+        kept = ctx.extras.get("kept_streams")
+        if kept is None or kept.shape[0] < self.place + 2:
+            raise ValueError("the model's plan must keep the streams of a step for layers that mix earlier results")
+        state = None
+        if self.conv_taps > 1:
+            *views, state = cache
+            cache = views[0] if len(views) == 1 else (tuple(views) if views else None)
+        a = ctx.extras.pop("normed_input", None)
+        if a is None:
+            a = self.norm_in.forward(h, None, self.input_dtype(ctx))
+        if self.conv_taps:
+            g = F.causal_conv(a, self.conv, state, ctx.tok_pos, ctx.tok_seq, ctx.cu_q, ctx.slots, ctx.dtype)
+            if state is not None and not ctx.extras.get("cache_read_only", False):
+                F.conv_state(a, state, ctx.cu_q, ctx.slots, ctx.n_seqs)
+        else:
+            g = a
+        y = self.mixer.forward(g, ctx, cache)
+        # the embedding output is one of the kept streams: the first layer's sums go to a stream of their own
+        stream = torch.empty_like(h) if h.data_ptr() == kept.data_ptr() else h
+        follower = self.next_block
+        if self.feed_forward is None:
+            return self._close(h, y, self.norm_out_1, self.scale_1, kept, follower, ctx, stream), None
+        _, z = F.branch_merge(h, y, self.norm_out_1.weight, self.norm_out_1.eps, self.scale_1,
+                              next_weight=self.norm_mid.weight, next_eps=self.norm_mid.eps, next_dtype=ctx.dtype, x_out=stream)
+        y = self.feed_forward.forward(z, ctx)
+        return self._close(stream, y, self.norm_out_2, self.scale_2, kept, follower, ctx, stream), None
+
+    def _close(self, x, y, norm, scale, kept, follower, ctx, stream):
+        """The layer's last sum: the result is kept, the depth mix goes on, and the next layer's head norm is formed."""
+        next_weight = next_eps = None
+        next_dtype = torch.float32
+        if follower is not None:
+            next_weight, next_eps, next_dtype = follower.norm_in.weight, follower.norm_in.eps, follower.input_dtype(ctx)
+        _, z = F.branch_merge(x, y, norm.weight, norm.eps, scale, kept=kept, n_kept=self.place + 1, mix=self.mix,
+                              next_weight=next_weight, next_eps=next_eps or 0.0, next_dtype=next_dtype, x_out=stream)
+        if z is not None:
+            ctx.extras["normed_input"] = z
+        return stream
+
+
+register_part("block", "sandwich", SandwichBlock)

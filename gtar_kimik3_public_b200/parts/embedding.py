@@ -13,18 +13,19 @@ from .base import Part, TensorSpec
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.weight_name = weight_name
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.weight_name: TensorSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.weight_name].contiguous()
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        return F.embed_rows(self.weight, ids)
+    def forward(self, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        return F.embed_rows(self.weight, ids, out)
 
 
 class OutputHead(Part):

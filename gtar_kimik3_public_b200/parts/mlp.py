@@ -56,3 +56,32 @@ class SwiGLUFeedForward(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+
+
+class GeluFeedForward(FeedForward):
+    """``down(gelu(up(x)))`` with the tanh form of GELU, ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``; no gate,
+    no biases.  Tensor names are given by the builder (defaults ``up.weight`` / ``down.weight``)."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, up_name: str = "up.weight", down_name: str = "down.weight"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.up_name: TensorSpec((i, h)), self.down_name: TensorSpec((h, i))}
+
+    def load(self, tensors):
+        self.w_up = tensors[self.up_name].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+        return linear(F.gelu_tanh(linear(x, self.w_up)), self.w_down)
+
+
+register_part("feed_forward", "gelu", GeluFeedForward)

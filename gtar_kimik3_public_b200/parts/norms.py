@@ -12,16 +12,25 @@ from .base import Norm, TensorSpec, register_part
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, weight_offset: float = 0.0, weight_name: str = "weight"):
+        """``weight_offset``: the file stores the weight minus this number (1.0 for a weight kept around zero); the
+        sum is formed once at load, in 32-bit, and the kernels multiply by it as by any weight.  ``weight_name``: the
+        tensor's name relative to the part ("" where the part's prefix is the whole name)."""
         self.size = int(size)
         self.eps = float(eps)
+        self.weight_offset = float(weight_offset)
+        self.weight_name = weight_name
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.size,), "vector")}
+        init = (0.0, 0.1) if self.weight_offset else None
+        return {self.weight_name: TensorSpec((self.size,), "vector", init=init)}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        weight = tensors[self.weight_name]
+        if self.weight_offset:
+            weight = weight.float() + self.weight_offset
+        self.weight = weight.contiguous()
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()

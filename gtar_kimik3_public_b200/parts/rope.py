@@ -8,6 +8,8 @@ and are made on the device once, for as many positions as the cache can hold.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionEncoding, register_part
@@ -28,6 +30,10 @@ class RotaryEncoding(PositionEncoding):
     def inv_freq(self) -> torch.Tensor:
         return 1.0 / (self.base ** (torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim))
 
+    def magnitude(self) -> float:
+        """A factor on every cosine and sine (1 for the plain rotation)."""
+        return 1.0
+
     def prepare(self, max_position: int, device: torch.device) -> None:
         have = 0 if self.cos is None else self.cos.shape[0]
         if self.cos is not None and self.cos.device == device and have > max_position:
@@ -39,8 +45,40 @@ class RotaryEncoding(PositionEncoding):
         n = max(max_position + 1, 2 * have, 64)
         positions = torch.arange(n, dtype=torch.float32, device=device)
         freqs = positions[:, None] * self.inv_freq().to(device)[None, :]
-        self.cos = freqs.cos().contiguous()
-        self.sin = freqs.sin().contiguous()
+        magnitude = self.magnitude()
+        self.cos = (freqs.cos() * magnitude).contiguous() if magnitude != 1.0 else freqs.cos().contiguous()
+        self.sin = (freqs.sin() * magnitude).contiguous() if magnitude != 1.0 else freqs.sin().contiguous()
+
+
+class ScaledRotaryEncoding(RotaryEncoding):
+    """Rotation whose slow frequencies are stretched for contexts longer than the ``original`` one (the YaRN rule).
+
+    With ``d(t) = dim * ln(original / (2 pi t)) / (2 ln base)`` the index of the frequency that makes ``t`` turns over
+    the original context, ``lo = max(floor(d(fast)), 0)``, ``hi = min(ceil(d(slow)), dim - 1)`` and ``ramp_i =
+    clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, frequency ``i`` becomes ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``:
+    fast frequencies stay, slow ones are divided by ``factor``, a linear blend between.  Every cosine and sine is
+    multiplied by ``0.1 ln(factor) + 1``.
+    """
+
+    def __init__(self, dim: int, base: float, factor: float, original: float, fast: float, slow: float):
+        super().__init__(dim, base)
+        if not factor > 0 or not original > 0 or not fast > 0 or not slow > 0:
+            raise ValueError("scaling factor, original context and the two turn counts must be positive")
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+
+    def _turn_index(self, turns: float) -> float:
+        return self.dim * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+    def inv_freq(self) -> torch.Tensor:
+        plain = super().inv_freq()
+        lo = max(math.floor(self._turn_index(self.fast)), 0)
+        hi = min(math.ceil(self._turn_index(self.slow)), self.dim - 1)
+        ramp = ((torch.arange(self.dim // 2, dtype=torch.float32) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return plain / self.factor * ramp + plain * (1.0 - ramp)
+
+    def magnitude(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0
 
 
 register_part("position", "rope", RotaryEncoding)
+register_part("position", "rope_scaled", ScaledRotaryEncoding)

@@ -68,3 +68,7 @@ def _ensure_builtin() -> None:
     from .models.transformer import build_transformer_plan
 
     register_architecture(TransformerConfig.ARCH_NAMES, TransformerConfig, build_transformer_plan)
+    from .config.dasusun import DasusunConfig
+    from .models.dasusun import build_dasusun_plan
+
+    register_architecture(DasusunConfig.ARCH_NAMES, DasusunConfig, build_dasusun_plan)

@@ -30,6 +30,9 @@ def random_tensors(specs, seed: int, std: float, matrix_dtype=torch.bfloat16, ve
             continue
         if spec.kind == "table":
             out[name] = torch.randint(0, 2**15, spec.shape, generator=gen, dtype=torch.int32)
+        elif spec.init is not None:
+            keep = vector_dtype if spec.kind == "vector" else matrix_dtype
+            out[name] = (spec.init[0] + spec.init[1] * torch.randn(spec.shape, generator=gen)).to(keep)
         elif spec.kind == "vector":
             out[name] = (1.0 + 0.1 * torch.randn(spec.shape, generator=gen)).to(vector_dtype)
         else:
@@ -81,6 +84,9 @@ def load_random_weights(model, seed: int, std: float | None = None) -> None:
             continue
         if spec.kind == "table":
             tensors[name] = torch.randint(0, 2**15, spec.shape, generator=gen, dtype=torch.int32, device=model.device)
+        elif spec.init is not None:
+            keep = stored_dtype_rule(torch.float32 if spec.kind == "vector" else torch.bfloat16, spec.kind, model.dtype)
+            tensors[name] = (spec.init[0] + spec.init[1] * torch.randn(spec.shape, generator=gen, device=model.device)).to(keep)
         elif spec.kind == "vector":
             keep = stored_dtype_rule(torch.float32, spec.kind, model.dtype)
             tensors[name] = (1.0 + 0.1 * torch.randn(spec.shape, generator=gen, device=model.device)).to(keep)

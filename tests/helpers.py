@@ -88,7 +88,8 @@ def poison(engine) -> None:
     """Fills every page with NaN so that a read of a place no step has written shows in the logits."""
     for group in engine.cache.kv_groups:
         group.k.fill_(float("nan"))
-        group.v.fill_(float("nan"))
+        if group.v is not None:
+            group.v.fill_(float("nan"))
 
 
 def check_against_plain(tag: str, dtype: str, tokens: list[int], places: list[int], got: torch.Tensor, what: str) -> None:
