@@ -1,0 +1,79 @@
+"""Shared pieces of the Dasusun tests: tiny model folders written by the library's random-weights mode, the plain
+implementation's logits for a request, and the error rules."""
+
+from __future__ import annotations
+
+import tempfile
+from pathlib import Path
+
+import torch
+
+from tests.dasusun_configs import DAS_CONFIGS
+from tests.plain import dasusun as plain
+from tests.plain.weights import read_safetensors
+
+WEIGHT_STD = 0.08
+_folders: dict = {}
+_weights: dict = {}
+_logits: dict = {}
+
+
+def das_folder(tag: str, seed: int = 0) -> Path:
+    key = (tag, seed)
+    if key not in _folders:
+        from gtar_kimik3_public_b200.registry import config_from_dict
+        from gtar_kimik3_public_b200.weights import write_random_model
+
+        holder = tempfile.TemporaryDirectory(prefix=f"gtar_test_{tag}_")
+        write_random_model(holder.name, config_from_dict(DAS_CONFIGS[tag]), seed, std=WEIGHT_STD)
+        _folders[key] = holder
+    return Path(_folders[key].name)
+
+
+def das_weights(tag: str, seed: int = 0) -> dict:
+    key = (tag, seed)
+    if key not in _weights:
+        _weights[key] = read_safetensors(das_folder(tag, seed) / "model.safetensors")
+    return _weights[key]
+
+
+def das_requests(tag: str, lengths, seed: int = 7) -> list[list[int]]:
+    gen = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, DAS_CONFIGS[tag]["vocab"], (n,), generator=gen).tolist() for n in lengths]
+
+
+def das_plain_logits(tag: str, tokens, mode: str = "f64", seed: int = 0) -> torch.Tensor:
+    key = (tag, tuple(tokens), mode, seed)
+    if key not in _logits:
+        ids = torch.tensor(list(tokens))
+        if mode == "lowp":
+            plain.LOWP = torch.bfloat16
+            try:
+                out = plain.forward(ids, das_weights(tag, seed), DAS_CONFIGS[tag], torch.float32)
+            finally:
+                plain.LOWP = None
+        else:
+            out = plain.forward(ids, das_weights(tag, seed), DAS_CONFIGS[tag], torch.float64 if mode == "f64" else torch.float32)
+        _logits[key] = out
+    return _logits[key]
+
+
+def das_engine(tag: str, dtype: str, max_tokens: int, seed: int = 0, max_seqs: int | None = None, **options):
+    from gtar_kimik3_public_b200.engine import Engine
+    from gtar_kimik3_public_b200.generate import load
+
+    return Engine(load(das_folder(tag, seed), dtype, "cuda:0"), max_tokens, max_seqs=max_seqs, **options)
+
+
+def das_check(tag: str, dtype: str, tokens, places, got: torch.Tensor, what: str) -> None:
+    """float32: within 2e-4 of the float64 oracle on logits of size O(1).  bfloat16: the error against the oracle may be
+    at most twice that of the plain implementation with bfloat16 matrix products, plus 1e-3."""
+    got = got.detach().double().cpu()
+    assert torch.isfinite(got).all(), f"{what}: logits are not finite"
+    oracle = das_plain_logits(tag, tokens, "f64")[places]
+    err = (got - oracle).abs().max().item()
+    if dtype == "float32":
+        assert err < 2e-4, f"{what}: float32 logits differ from the oracle by {err:.3e}"
+    else:
+        yard = (das_plain_logits(tag, tokens, "lowp")[places].double() - oracle).abs().max().item()
+        assert err <= 2 * yard + 1e-3, f"{what}: bfloat16 error {err:.3e} exceeds twice the yardstick {yard:.3e}"
