@@ -1,0 +1,377 @@
+// Attention over latent rows on the tensor cores (bfloat16 operands, 32-bit scores, softmax and sums): the kernel
+// for prompts and for single-token steps of layers that keep one row  [c (rank) | k_rot (rot)]  per position for all
+// heads (see attention_latent.cu for the algebra).  All heads read the SAME rows, so a block's sixteen query rows are
+// (token, head) pairs of one sequence, head running fastest: with sixteen heads a tile is one token, with four heads
+// four consecutive tokens, whose key ranges differ by a few positions only.
+//
+// A block = 16 query rows x 4 warps.  Keys come a page (64 positions) at a time through a two-stage cp.async ring;
+// rows outside the tile's key range are filled with zeros (a page's unwritten places may hold anything).  Per page:
+//   scores:  warp w forms  S[16 x 16 keys 16w..16w+15]  over the whole row width (rank + rot), masks what its rows
+//            must not see, and posts its rows' maxima;
+//   softmax: with the maxima of all four warps every warp rescales ITS columns of the output, writes its
+//            probabilities (bfloat16) into the shared P tile [16 x 64] and posts its partial row sums;
+//   output:  warp w adds  P[16 x 64] V[64 x its rank/4 columns]  to its accumulator; V is the first `rank` entries of
+//            the same rows, read transposed by ldmatrix.
+// So the wide output (rank up to 512) is spread over the warps (64 registers a thread at most) while the scores are
+// spread by keys; the P tile and two small arrays of row statistics are what the warps exchange.
+//
+// Single-token steps have few tiles; `splits` blocks then share a tile's pages and leave partial results
+// (maximum, sum, unnormalised output) in scratch, merged by a second kernel in split order.
+//
+// The query tile is [carried part (rank) | own rotated part (rot)]; the rotation of the own part is done while the
+// tile is staged (32-bit, tables of cos and sin).  Sizes: rank a multiple of 64 up to 512, rot a multiple of 16,
+// pages of 64 positions.
+
+#include "attention_mma.cuh"
+
+namespace {
+
+using namespace attn;
+
+constexpr int WARPS = 4, THREADS = WARPS * 32, ROWS = 16;
+constexpr int P_STRIDE = PAGE + 8;  // bfloat16 elements: 144 bytes a row, so that ldmatrix rows fall into different banks
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct TiledArgs {
+    const __nv_bfloat16* q_carried; long long qc_tok, qc_head;
+    const __nv_bfloat16* q_raw; int q_raw_dim, q_rot_at;
+    const float* cos_table; const float* sin_table;
+    const __nv_bfloat16* pages;
+    __nv_bfloat16* out; long long out_tok, out_head;
+    float* part_o; float* part_ml;  // [split, global row, rank] and [split, global row, 2] when splits > 1
+    const int* tok_pos; const int* cu_q; const int* slots; const int* block_table;
+    int n_heads, rank, rot, rot_dims, max_pages, splits, n_rows_total, window;
+    float scale;
+};
+
+template <int NT>  // 8-column tiles of the output a warp owns at most: rank / 32 <= NT
+__global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const TiledArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.y, tile = blockIdx.x, split = blockIdx.z;
+    const int first_tok = a.cu_q[seq], n_tok = a.cu_q[seq + 1] - first_tok;
+    const int n_rows = n_tok * a.n_heads;
+    if (tile * ROWS >= n_rows) return;
+    const int width = a.rank + a.rot;
+    const int stride = width + 8;  // elements; rows of (width + 8) * 2 bytes: an odd number of 16-byte pieces
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* k_s = q_s + ROWS * stride;                 // two stages of PAGE rows
+    __nv_bfloat16* p_s = k_s + 2 * PAGE * stride;             // [ROWS][P_STRIDE]
+    float* stat_max = reinterpret_cast<float*>(p_s + ROWS * P_STRIDE);  // [2][WARPS][ROWS]
+    float* stat_sum = stat_max + 2 * WARPS * ROWS;                       // [2][WARPS][ROWS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+
+    // ---- the tile's rows: row r is head (r0 + r) % H of token (r0 + r) / H of the sequence's step
+    const int r0 = tile * ROWS;
+    const int last_row = min(r0 + ROWS, n_rows) - 1;
+    const int tok_lo = r0 / a.n_heads, tok_hi = last_row / a.n_heads;
+    const int pos_lo = a.tok_pos[first_tok + tok_lo], pos_hi = a.tok_pos[first_tok + tok_hi];
+    const int key_lo = (a.window > 0 && pos_lo - a.window + 1 > 0) ? pos_lo - a.window + 1 : 0;  // first key any row sees
+    // this thread's two rows (g and g + 8): their positions, -1 for rows beyond the sequence's last
+    int my_pos[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = r0 + g + 8 * i;
+        my_pos[i] = r < n_rows ? a.tok_pos[first_tok + r / a.n_heads] : -1;
+    }
+    // ---- the pages this block walks
+    const int page_first = key_lo / PAGE, page_last = pos_hi / PAGE;
+    const int n_pages_all = page_last - page_first + 1;
+    const int per_split = (n_pages_all + a.splits - 1) / a.splits;
+    const int my_first = page_first + split * per_split;
+    const int my_last = min(my_first + per_split - 1, page_last);
+    const int* table = a.block_table + (size_t)a.slots[seq] * a.max_pages;
+    const int pieces = width / 8;  // 16-byte pieces of a row
+
+    auto load_page = [&](int stage, int page_index) {
+        const int page = table[page_index];
+        const __nv_bfloat16* src = a.pages + (size_t)page * PAGE * width;
+        __nv_bfloat16* dst = k_s + (size_t)stage * PAGE * stride;
+        const int j0 = page_index * PAGE;
+        for (int i = tid; i < PAGE * pieces; i += THREADS) {
+            const int row = i / pieces, piece = i - row * pieces;
+            const int j = j0 + row;
+            cp_async_16(dst + (size_t)row * stride + piece * 8, src + (size_t)row * width + piece * 8, j >= key_lo && j <= pos_hi);
+        }
+    };
+    if (my_first <= my_last) load_page(0, my_first);
+    cp_async_commit();
+
+    // ---- stage the query tile: carried part as it is, own part rotated
+    for (int i = tid; i < ROWS * width; i += THREADS) {
+        const int r = i / width, d = i - r * width;
+        const int row = r0 + r;
+        float v = 0.f;
+        if (row < n_rows) {
+            const int t = first_tok + row / a.n_heads, h = row % a.n_heads;
+            if (d < a.rank) {
+                v = __bfloat162float(a.q_carried[(size_t)t * a.qc_tok + (size_t)h * a.qc_head + d]);
+            } else {
+                const int e = d - a.rank;
+                const __nv_bfloat16* own = a.q_raw + ((size_t)t * a.n_heads + h) * a.q_raw_dim + a.q_rot_at;
+                v = __bfloat162float(own[e]);
+                if (e < a.rot_dims) {
+                    const int half = a.rot_dims >> 1, f = e < half ? e : e - half;
+                    const int pos = a.tok_pos[t];
+                    const float c = a.cos_table[(size_t)pos * half + f], s = a.sin_table[(size_t)pos * half + f];
+                    const float other = __bfloat162float(own[e < half ? e + half : e - half]);
+                    v = e < half ? v * c - other * s : v * c + other * s;
+                }
+            }
+        }
+        q_s[(size_t)r * stride + d] = __float2bfloat16_rn(v);
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int nt_used = a.rank / 32;          // this warp's 8-column tiles (even: rank is a multiple of 64)
+    const int col0 = warp * (a.rank / 4);     // its first output column
+    const float sl2 = a.scale * LOG2E;
+    const int k_steps = width / 16;
+
+    for (int pi = my_first, it = 0; pi <= my_last; ++pi, ++it) {
+        const int stage = it & 1;
+        cp_async_wait<0>();
+        __syncthreads();  // the page (at the first turn also the query tile) is in shared memory, and every warp is done with the
+                          // other stage, the P tile and the statistics of the turn before
+        if (pi + 1 <= my_last) load_page(stage ^ 1, pi + 1);  // arrives under this turn's arithmetic
+        cp_async_commit();
+        const __nv_bfloat16* kt = k_s + (size_t)stage * PAGE * stride;
+        // ---- scores of this warp's 16 keys
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+        {
+            const __nv_bfloat16* q_lane = q_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
+            const __nv_bfloat16* k_lane = kt + (size_t)(warp * 16 + (lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                uint32_t qa[4], kb[4];
+                ldmatrix_x4(qa, q_lane + ks * 16);
+                ldmatrix_x4(kb, k_lane + ks * 16);
+                mma_16816(s[0], qa, kb[0], kb[1]);
+                mma_16816(s[1], qa, kb[2], kb[3]);
+            }
+        }
+        // ---- mask, and this warp's row maxima
+        const int j_base = pi * PAGE + warp * 16;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int i = c >> 1;  // row g (c = 0, 1) or g + 8 (c = 2, 3)
+                const int j = j_base + n * 8 + 2 * tg + (c & 1);
+                const bool seen = j <= my_pos[i] && (a.window == 0 || my_pos[i] - j < a.window);
+                s[n][c] = seen ? s[n][c] * sl2 : -INFINITY;
+                mx[i] = fmaxf(mx[i], s[n][c]);
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        }
+        float* smax = stat_max + stage * WARPS * ROWS;
+        float* ssum = stat_sum + stage * WARPS * ROWS;
+        if (tg == 0) {
+            smax[warp * ROWS + g] = mx[0];
+            smax[warp * ROWS + g + 8] = mx[1];
+        }
+        __syncthreads();
+        // ---- the rows' new maxima, probabilities, partial sums; rescale the accumulator
+        float corr[2], m_new[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            float m = m_run[i];
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) m = fmaxf(m, smax[w * ROWS + r]);
+            m_new[i] = m;
+            corr[i] = m == -INFINITY ? 1.f : exp2f(m_run[i] - m);
+            m_run[i] = m;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            float p[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int i = c >> 1;
+                p[c] = m_new[i] == -INFINITY ? 0.f : exp2f(s[n][c] - m_new[i]);
+                sum[i] += p[c];
+            }
+            const int col = warp * 16 + n * 8 + 2 * tg;
+            *reinterpret_cast<uint32_t*>(p_s + (size_t)g * P_STRIDE + col) = pack_bf16(p[0], p[1]);
+            *reinterpret_cast<uint32_t*>(p_s + (size_t)(g + 8) * P_STRIDE + col) = pack_bf16(p[2], p[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+            sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+        }
+        if (tg == 0) {
+            ssum[warp * ROWS + g] = sum[0];
+            ssum[warp * ROWS + g + 8] = sum[1];
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+            if (n < nt_used) {
+                o[n][0] *= corr[0]; o[n][1] *= corr[0];
+                o[n][2] *= corr[1]; o[n][3] *= corr[1];
+            }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) t += ssum[w * ROWS + r];
+            l_run[i] = l_run[i] * corr[i] + t;
+        }
+        // ---- output: P [16 x 64] times this warp's columns of V
+        {
+            const __nv_bfloat16* p_lane = p_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * P_STRIDE + (lane >> 4) * 8;
+            const __nv_bfloat16* v_lane = kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + col0 + (lane >> 4) * 8;
+#pragma unroll
+            for (int kk = 0; kk < PAGE / 16; ++kk) {
+                uint32_t pa[4];
+                ldmatrix_x4(pa, p_lane + kk * 16);
+#pragma unroll
+                for (int n = 0; n < NT; n += 2)
+                    if (n < nt_used) {
+                        uint32_t vb[4];
+                        ldmatrix_x4_trans(vb, v_lane + (size_t)kk * 16 * stride + n * 8);
+                        mma_16816(o[n], pa, vb[0], vb[1]);
+                        mma_16816(o[n + 1], pa, vb[2], vb[3]);
+                    }
+            }
+        }
+        // the next turn's first barrier stands between these reads of the page and of P and their next writes
+    }
+    cp_async_wait<0>();
+
+    // ---- results
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = r0 + g + 8 * i;
+        if (row >= n_rows) continue;
+        const int t = first_tok + row / a.n_heads, h = row % a.n_heads;
+        if (a.splits == 1) {
+            const float inv = 1.f / l_run[i];
+            __nv_bfloat16* dst = a.out + (size_t)t * a.out_tok + (size_t)h * a.out_head + col0;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                if (n < nt_used)
+                    *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * tg) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+        } else {
+            const size_t grow = (size_t)split * a.n_rows_total + (size_t)t * a.n_heads + h;
+            float* dst = a.part_o + grow * a.rank + col0;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                if (n < nt_used) *reinterpret_cast<float2*>(dst + n * 8 + 2 * tg) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+            if (warp == 0 && tg == 0) {
+                a.part_ml[grow * 2] = m_run[i];
+                a.part_ml[grow * 2 + 1] = l_run[i];
+            }
+        }
+    }
+}
+
+// One warp per (token, head): the splits' partial results in split order.  Maxima are in the exponent-of-two scale
+// of the kernel above.
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, long long out_tok, long long out_head, int n_rows_total,
+                                    int n_heads, int rank, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows_total) return;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)s * n_rows_total + row) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[((size_t)s * n_rows_total + row) * 2];
+        if (ms != -INFINITY) l += part_ml[((size_t)s * n_rows_total + row) * 2 + 1] * exp2f(ms - m);
+    }
+    const int t = row / n_heads, h = row % n_heads;
+    __nv_bfloat16* dst = out + (size_t)t * out_tok + (size_t)h * out_head;
+    for (int d = lane; d < rank; d += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[((size_t)s * n_rows_total + row) * 2];
+            if (ms != -INFINITY) acc += part_o[((size_t)s * n_rows_total + row) * rank + d] * exp2f(ms - m);
+        }
+        dst[d] = __float2bfloat16_rn(acc / l);
+    }
+}
+
+template <int NT>
+int launch_tiled(const TiledArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+    static bool prepared = false;
+    if (!prepared) {
+        cudaFuncSetAttribute(attention_latent_tiled_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        prepared = true;
+    }
+    gk_launch(attention_latent_tiled_kernel<NT>, grid, dim3(THREADS), smem, s, a);
+    return 0;
+}
+
+}  // namespace
+
+// Shared memory the kernel needs for rows of `width` = rank + rot.
+GK_EXPORT int gk_attention_latent_tiled_smem(int width) {
+    return (ROWS + 2 * PAGE) * (width + 8) * 2 + ROWS * P_STRIDE * 2 + 4 * WARPS * ROWS * 4;
+}
+
+GK_EXPORT int gk_attention_latent_tiled(const void* q_carried, long long qc_tok, long long qc_head, const void* q_raw,
+                                        int q_raw_dim, int q_rot_at, const float* cos_table, const float* sin_table,
+                                        const void* pages, void* out, long long out_tok, long long out_head, float* part_o,
+                                        float* part_ml, const int* tok_pos, const int* cu_q, const int* slots,
+                                        const int* block_table, int n_tokens, int n_seqs, int max_q_len, int n_heads, int rank,
+                                        int rot, int rot_dims, int max_pages, int page_size, float scale, int window, int splits,
+                                        void* stream) {
+    GK_REQUIRE(n_tokens >= 0 && n_seqs > 0 && max_q_len > 0 && n_heads > 0, "attention_latent_tiled: bad sizes");
+    GK_REQUIRE(rank > 0 && rank % 64 == 0 && rank <= 512 && rot >= 0 && rot % 16 == 0,
+               "attention_latent_tiled: rank %d must be a multiple of 64 up to 512 and rot %d a multiple of 16", rank, rot);
+    GK_REQUIRE(rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0, "attention_latent_tiled: bad rotation sizes");
+    GK_REQUIRE(q_rot_at >= 0 && q_rot_at + rot <= q_raw_dim, "attention_latent_tiled: the rotated part lies outside the head");
+    GK_REQUIRE(page_size == PAGE, "attention_latent_tiled: pages must hold %d positions", PAGE);
+    GK_REQUIRE(window >= 0 && splits >= 1 && splits <= 65535, "attention_latent_tiled: bad window or splits");
+    GK_REQUIRE(splits == 1 || (part_o && part_ml), "attention_latent_tiled: splits need scratch");
+    GK_REQUIRE(((uintptr_t)pages & 15) == 0 && ((uintptr_t)out & 3) == 0 && out_tok % 2 == 0 && out_head % 2 == 0,
+               "attention_latent_tiled: misaligned pages or output");
+    if (n_tokens == 0) return GK_OK;
+    const size_t smem = (size_t)gk_attention_latent_tiled_smem(rank + rot);
+    GK_REQUIRE(smem <= 200 * 1024, "attention_latent_tiled: rows of %d do not fit in shared memory", rank + rot);
+    const long long tiles = ((long long)max_q_len * n_heads + ROWS - 1) / ROWS;
+    GK_REQUIRE(tiles <= 2147483647LL && n_seqs <= 65535, "attention_latent_tiled: too many tiles or sequences");
+    TiledArgs a;
+    a.q_carried = (const __nv_bfloat16*)q_carried; a.qc_tok = qc_tok; a.qc_head = qc_head;
+    a.q_raw = (const __nv_bfloat16*)q_raw; a.q_raw_dim = q_raw_dim; a.q_rot_at = q_rot_at;
+    a.cos_table = cos_table; a.sin_table = sin_table; a.pages = (const __nv_bfloat16*)pages;
+    a.out = (__nv_bfloat16*)out; a.out_tok = out_tok; a.out_head = out_head; a.part_o = part_o; a.part_ml = part_ml;
+    a.tok_pos = tok_pos; a.cu_q = cu_q; a.slots = slots; a.block_table = block_table;
+    a.n_heads = n_heads; a.rank = rank; a.rot = rot; a.rot_dims = rot_dims; a.max_pages = max_pages; a.splits = splits;
+    a.n_rows_total = n_tokens * n_heads; a.window = window; a.scale = scale;
+    dim3 grid((unsigned)tiles, (unsigned)n_seqs, (unsigned)splits);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = rank / 32;
+    if (nt <= 2) launch_tiled<2>(a, grid, smem, s);
+    else if (nt <= 4) launch_tiled<4>(a, grid, smem, s);
+    else if (nt <= 8) launch_tiled<8>(a, grid, smem, s);
+    else launch_tiled<16>(a, grid, smem, s);
+    GK_CHECK_LAUNCH("attention_latent_tiled");
+    if (splits > 1) {
+        const int rows = n_tokens * n_heads;
+        gk_launch(latent_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml,
+                  (__nv_bfloat16*)out, out_tok, out_head, rows, n_heads, rank, splits);
+        GK_CHECK_LAUNCH("latent_merge");
+    }
+    return GK_OK;
+}

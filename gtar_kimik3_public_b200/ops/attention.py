@@ -64,13 +64,21 @@ def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: i
     return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window)
 
 
+# "0" sends bfloat16 latent attention through the exact kernel too (for measurements and for telling the kernels apart)
+LATENT_TILED = os.environ.get("GTAR_B200_LATENT_TILED", "1") != "0"
+
+
 def latent_attention(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_at: int, rot: int, rot_dims: int, cos, sin,
                      cache: F.PagedRows, ctx, scale: float, window: int, out: torch.Tensor) -> torch.Tensor:
     """Attention of the step's queries over each sequence's cached latent rows (the new tokens' own are already
     written): ``q_carried [n_tokens, n_heads, rank]`` is the unrotated query carried into the latent, ``q_raw`` holds
     each head's own part to rotate at ``q_rot_at``; ``out [n_tokens, n_heads, rank]`` is the weighted sum of latents."""
-    if q_raw.dtype == torch.bfloat16 and F.latent_tiled_ok(q_carried.shape[1], q_carried.shape[2], rot, cache):
-        return F.attention_latent_tiled(q_carried, q_raw, q_rot_at, rot, rot_dims, cos, sin, cache, ctx.tok_pos, ctx.tok_seq,
-                                        ctx.cu_q, ctx.slots, scale, window, out, ctx.max_q_len)
+    if LATENT_TILED and q_raw.dtype == torch.bfloat16 and F.latent_tiled_ok(q_carried.shape[1], q_carried.shape[2], rot, cache):
+        splits = 1
+        if ctx.all_single:
+            splits = F.latent_splits(ctx.n_seqs, q_carried.shape[1], ctx.typical_kv_len or ctx.max_kv_len, window,
+                                     F.sm_count(q_raw.device))
+        return F.attention_latent_tiled(q_carried, q_raw, q_rot_at, rot, rot_dims, cos, sin, cache, ctx.tok_pos, ctx.cu_q,
+                                        ctx.slots, scale, window, out, ctx.n_seqs, ctx.max_q_len, splits)
     return F.attention_latent_exact(q_carried, q_raw, q_rot_at, rot, rot_dims, cos, sin, cache, ctx.tok_pos, ctx.tok_seq,
                                     ctx.slots, scale, window, out)

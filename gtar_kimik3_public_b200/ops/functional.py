@@ -1186,6 +1186,48 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     return out
 
 
+LATENT_TILED_MAX_SPLITS = 16
+
+
 def latent_tiled_ok(n_heads: int, rank: int, rot: int, cache: PagedRows) -> bool:
-    """Whether the tensor-core kernel takes the layer (none is built for these rows yet: the exact kernel runs)."""
-    return False
+    """Whether the tensor-core kernel takes the layer: bfloat16 rows in pages of 64, the latent a multiple of 64 up to
+    512, the rotated part a multiple of 16 (other sizes run on the exact kernel)."""
+    return (cache.rows.dtype == torch.bfloat16 and cache.page_size == 64 and rank % 64 == 0 and 0 < rank <= 512 and rot % 16 == 0
+            and (16 + 128) * (rank + rot + 8) * 2 + 4096 <= 200 * 1024)
+
+
+def latent_splits(n_seqs: int, n_heads: int, kv_len: int, window: int, sms: int) -> int:
+    """Into how many blocks a tile's pages are cut in a single-token step: enough blocks for the device, at most one
+    per page and ``LATENT_TILED_MAX_SPLITS``."""
+    tiles = n_seqs * -(-n_heads // 16)
+    span = min(kv_len, window) if window else kv_len
+    pages = span // 64 + 1
+    return max(1, min(pages, (2 * sms) // max(tiles, 1), LATENT_TILED_MAX_SPLITS))
+
+
+def attention_latent_tiled(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_at: int, rot: int, rot_dims: int,
+                           cos: torch.Tensor | None, sin: torch.Tensor | None, cache: PagedRows, tok_pos: torch.Tensor,
+                           cu_q: torch.Tensor, slots: torch.Tensor, scale: float, window: int, out: torch.Tensor, n_seqs: int,
+                           max_q_len: int, splits: int = 1) -> torch.Tensor:
+    """As ``attention_latent_exact``, on the tensor cores (bfloat16).  A sequence's tokens of the step must be at
+    consecutive rows in rising positions.  ``splits`` > 1 cuts every tile's pages among that many blocks (steps of few
+    tokens); the partial results go through scratch made here."""
+    require_device(q_raw.device)
+    _check(q_raw, "q_raw", torch.bfloat16, 3)
+    n, heads, raw_dim = q_raw.shape
+    rank = q_carried.shape[2]
+    for name, t in (("q_carried", q_carried), ("out", out)):
+        if t.dtype != torch.bfloat16 or tuple(t.shape) != (n, heads, rank) or t.stride(2) != 1:
+            raise KernelError(f"{name} must be bfloat16 [{n}, {heads}, {rank}] with a contiguous last axis")
+    _check(cache.rows, "cache rows", torch.bfloat16, 3)
+    if cache.rows.shape[2] != rank + rot:
+        raise KernelError(f"cache rows of {cache.rows.shape[2]} are not {rank} + {rot}")
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((splits, n * heads, rank), dtype=torch.float32, device=q_raw.device)
+        part_ml = torch.empty((splits, n * heads, 2), dtype=torch.float32, device=q_raw.device)
+    call("gk_attention_latent_tiled", ptr(q_carried), q_carried.stride(0), q_carried.stride(1), ptr(q_raw), raw_dim, int(q_rot_at),
+         ptr(cos), ptr(sin), ptr(cache.rows), ptr(out), out.stride(0), out.stride(1), ptr(part_o), ptr(part_ml), ptr(tok_pos),
+         ptr(cu_q), ptr(slots), ptr(cache.block_table), n, int(n_seqs), int(max_q_len), heads, rank, rot, rot_dims,
+         cache.max_pages, cache.page_size, float(scale), int(window), int(splits), stream_ptr())
+    return out

@@ -42,6 +42,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_conv_state": [P, P, P, P, I, I, I, P],
     "gk_gelu_tanh": [P, P, I, L, P],
     "gk_latent_prepare": [P, I, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+    "gk_attention_latent_tiled": [P, L, L, P, I, I, P, P, P, P, L, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_latent_exact": [P, L, L, P, I, I, P, P, P, P, L, L, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],

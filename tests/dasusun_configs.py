@@ -53,4 +53,16 @@ DAS_D = copy.deepcopy(DAS_B)  # no convolution at all
 del DAS_D["canon"]
 DAS_D["layers"] = DAS_D["layers"][:2]
 
-DAS_CONFIGS = {"das_a": DAS_A, "das_b": DAS_B, "das_c": DAS_C, "das_d": DAS_D}
+# Sizes the tensor-core attention kernel takes in bfloat16 (latents of 64 and 128, rotated parts of 16 and 32), with head
+# counts that do not divide its sixteen-row tiles and one above sixteen.
+DAS_E = {
+    "architecture": "Dasusun", "vocab": 256, "width": 128, "norm": {"eps": 1e-6}, "canon": {"taps": 3},
+    "layers": [
+        _layer(_mixer(3, 16, 16, 24, 64, 64, 40, 16, 250000.0, _SCALING_B), 256),
+        _layer(_mixer(20, 8, 32, 8, 32, 128, 130, 16, 10000.0, None), 128),
+        _layer(_mixer(5, 24, 16, 16, 48, 64, None, 16, 10000.0, _SCALING_A), None),
+        _layer(_mixer(16, 16, 16, 16, 64, 64, 64, 8, 1000.0, None), 192),
+    ],
+}
+
+DAS_CONFIGS = {"das_e": DAS_E, "das_a": DAS_A, "das_b": DAS_B, "das_c": DAS_C, "das_d": DAS_D}

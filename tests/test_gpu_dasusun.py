@@ -12,7 +12,7 @@ from tests.helpers import poison
 
 pytestmark = pytest.mark.gpu
 
-CASES = [(tag, dtype) for tag in ("das_a", "das_b", "das_c", "das_d") for dtype in ("float32", "bfloat16")]
+CASES = [(tag, dtype) for tag in ("das_a", "das_b", "das_c", "das_d", "das_e") for dtype in ("float32", "bfloat16")]
 LENGTHS = [1, 2, 3, 17, 64, 65, 90, 150]
 
 
@@ -114,7 +114,7 @@ def test_batch_equals_alone_in_float32(tag):
     assert torch.equal(together, torch.cat(alone))
 
 
-@pytest.mark.parametrize("tag,dtype", [("das_a", "bfloat16"), ("das_b", "float32")])
+@pytest.mark.parametrize("tag,dtype", [("das_a", "bfloat16"), ("das_b", "float32"), ("das_e", "bfloat16")])
 def test_graph_replay_matches_launches(tag, dtype):
     """Decode steps replayed from CUDA graphs give what the same steps give launch by launch."""
     (tokens,) = das_requests(tag, [90], seed=2)

@@ -165,7 +165,8 @@ def _attend_plain(q_full, rows, pos, window, scale, rank):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [0, 1, 40, 64, 65, 200])
-def test_latent_attention_one_key_decides(dtype, window):
+@pytest.mark.parametrize("heads,rank,rot", [(3, 48, 8), (5, 64, 16), (20, 128, 32)])
+def test_latent_attention_one_key_decides(dtype, window, heads, rank, rot):
     """Every cached row points its own way; each query is made to point at ONE chosen key, with a score far above
     the others, so that the output is that key's latent if the key is visible and something else if it is not.
     Targets: the query's own position, the key before it, the last key inside the window, the first outside, keys at
@@ -175,7 +176,7 @@ def test_latent_attention_one_key_decides(dtype, window):
     from gtar_kimik3_public_b200.parts.base import StepContext
 
     F = _f()
-    heads, rank, rot, rot_dims, dn = 3, 48, 8, 8, 16
+    rot_dims, dn = 8, 16  # the sizes with a latent of 64 or 128 go through the tensor-core kernel in bfloat16
     length, slot, scale = 300, 1, 0.25
     gen = torch.Generator().manual_seed(window)
     rows = torch.randn(length, rank + rot, generator=gen)
