@@ -564,6 +564,251 @@ def run_reference(args, device: str = "cuda:0", sizes: dict | None = None, promp
     }
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --compare dasusun: the Dasusun decoder beside the dense transformer at equal layer sizes (random weights drawn on the
+# device, the same prompts, the same engine): prefill and decode throughput, and the new design's kernels one by one
+# against their rooflines beside the like kernels of the transformer.
+def _dasusun_config(width, layers, heads, dim, rot, vdim, q_rank, kv_rank, window, ff, vocab):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "scale": (dim + rot) ** -0.5, "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    layer = {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Dasusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "layers": [layer] * layers, "initializer_range": 0.02, "max_position_embeddings": 4096}
+
+
+def _transformer_config(hidden, layers, heads, kv_heads, head_dim, ff, vocab):
+    return {"arch": "transformer", "vocab_size": vocab, "hidden_size": hidden, "intermediate_size": ff, "num_hidden_layers": layers,
+            "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim, "rms_norm_eps": 1e-6,
+            "rope_theta": 1000000.0, "tie_word_embeddings": True, "initializer_range": 0.02, "max_position_embeddings": 4096}
+
+
+COMPARE_SIZES = {
+    # name: (Dasusun sizes, transformer sizes); 8 layers each, vocabulary 32,768
+    "width1024": (dict(width=1024, layers=8, heads=16, dim=64, rot=32, vdim=64, q_rank=512, kv_rank=256, window=1024, ff=4096, vocab=32768),
+                  dict(hidden=1024, layers=8, heads=16, kv_heads=8, head_dim=128, ff=3072, vocab=32768)),
+    "width2048": (dict(width=2048, layers=8, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, window=2048, ff=8192, vocab=32768),
+                  dict(hidden=2048, layers=8, heads=16, kv_heads=8, head_dim=128, ff=6144, vocab=32768)),
+}
+
+
+def _device_model(raw: dict):
+    import torch
+
+    from gtar_kimik3_public_b200.models.model import Model
+    from gtar_kimik3_public_b200.registry import architecture, config_from_dict
+    from gtar_kimik3_public_b200.weights import load_random_weights
+
+    config = config_from_dict(raw)
+    model = Model(architecture(config.ARCH_NAMES[0]).build_plan(config), config, torch.bfloat16, "cuda:0")
+    load_random_weights(model, seed=0, std=0.02)
+    return model
+
+
+def _time_prefill_ms(model, tokens: int, warmup: int = 3, repeats: int = 5) -> float:
+    import torch
+
+    from gtar_kimik3_public_b200.cache import rounded_tokens
+    from gtar_kimik3_public_b200.engine import Engine, StepEntry
+
+    engine = Engine(model, rounded_tokens(tokens + 1), max_seqs=1)
+    prompt = random_prompts(1, tokens, model.vocab_size, seed=1)[0]
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + repeats):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            engine.step([StepEntry("p", prompt, [tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.end(["p"])
+            if i >= warmup:
+                times.append(begin.elapsed_time(end))
+    del engine
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def _dasusun_prefill_flops(d: dict, tokens: int) -> float:
+    w, h = d["width"], d["heads"]
+    per_token = 2 * (w * (d["q_rank"] + d["kv_rank"] + d["rot"]) + d["q_rank"] * h * (d["dim"] + d["rot"]) + h * d["dim"] * d["kv_rank"]
+                     + h * d["kv_rank"] * d["vdim"] + h * d["vdim"] * w + 2 * w * d["ff"])
+    seen = sum(min(t + 1, d["window"]) for t in range(tokens))
+    attention = h * seen * (2 * (d["kv_rank"] + d["rot"]) + 2 * d["kv_rank"])
+    return d["layers"] * (per_token * tokens + attention) + 2 * w * d["vocab"]
+
+
+def _transformer_prefill_flops(t: dict, tokens: int) -> float:
+    per_token = 2 * t["hidden"] * ((2 * t["heads"] + 2 * t["kv_heads"]) * t["head_dim"] + 3 * t["ff"])
+    attention = 4 * t["heads"] * t["head_dim"] * tokens * tokens / 2
+    return t["layers"] * (per_token * tokens + attention) + 2 * t["hidden"] * t["vocab"]
+
+
+def _event_ms(fn, warmup: int = 3, repeats: int = 10, flush=None, inner: int = 1) -> float:
+    """Median device time of one call.  ``flush``: a buffer larger than the L2 is written between the timed calls
+    (many-token kernels).  ``inner`` > 1: that many calls back to back in one timed region, replayed from a CUDA graph so
+    that the host's launch cost is not what is measured (few-token kernels, whose operands a step finds in the L2
+    anyway)."""
+    import torch
+
+    graph = None
+    if inner > 1:
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+    times = []
+    for i in range(warmup + repeats):
+        if flush is not None and graph is None:
+            flush.add_(1.0)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        if graph is None:
+            fn()
+        else:
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(begin.elapsed_time(end) / inner)
+    return statistics.median(times)
+
+
+def _kernel_table(d: dict, t: dict, peak: dict) -> dict:
+    """The new design's kernels alone, and the like kernels of the transformer, each with its share of its roofline
+    (bytes over the measured copy bandwidth, or FLOPs over the measured bfloat16 product rate, whichever is larger)."""
+    import torch
+
+    from gtar_kimik3_public_b200.ops import functional as F
+
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(48 << 20, dtype=torch.float32, device=dev)  # 192 MB: larger than the 126 MB L2
+    hbm, tflops = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+    out = {}
+
+    def record(name, ms, n_bytes, flops=0.0):
+        floor = max(n_bytes / hbm, flops / tflops) * 1e3
+        out[name] = {"us": round(ms * 1e3, 2), "roofline_us": round(floor * 1e3, 2), "frac": round(floor / ms, 4),
+                     "bound": "hbm" if n_bytes / hbm >= flops / tflops else "tensor"}
+
+    def tables(n, half):
+        angle = torch.arange(n, dtype=torch.float32, device=dev)[:, None] * torch.rand(half, device=dev)[None, :]
+        return angle.cos().contiguous(), angle.sin().contiguous()
+
+    for label, tokens, n_seqs in (("prefill_2048", 2048, 1), ("decode_b8_ctx2048", 8, 8)):
+        each = tokens // n_seqs
+        inner = 1 if n_seqs == 1 else 20
+        past = 0 if n_seqs == 1 else 2047
+        length = past + each
+        pages_each = -(-length // 64)
+        table = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).view(n_seqs, pages_each)
+        tok_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each)
+        tok_pos = (torch.arange(each, dtype=torch.int32, device=dev) + past).repeat(n_seqs)
+        cu_q = torch.arange(n_seqs + 1, dtype=torch.int32, device=dev) * each
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        kv_len = torch.full((n_seqs,), length, dtype=torch.int32, device=dev)
+        # ---- the new design
+        w, h, r, rot, dn = d["width"], d["heads"], d["kv_rank"], d["rot"], d["dim"]
+        rows = F.PagedRows(torch.randn(n_seqs * pages_each, 64, r + rot, device=dev).bfloat16() * 0.1, table)
+        cos, sin = tables(length, rot // 2)
+        carried = torch.randn(h, tokens, r, device=dev).bfloat16()
+        q_raw = torch.randn(tokens, h, dn + rot, device=dev).bfloat16()
+        mixed = torch.empty(h, tokens, r, dtype=torch.bfloat16, device=dev)
+        splits = 1 if n_seqs == 1 else F.latent_splits(n_seqs, h, length, d["window"], F.sm_count(dev))
+        seen = sum(min(p + 1, d["window"]) for p in range(past, length)) * n_seqs
+        flops = h * seen * (4 * r + 2 * rot)
+        n_bytes = 2 * (tokens * h * (2 * r + dn + rot) + n_seqs * min(length, d["window"] + each) * (r + rot))
+        ms = _event_ms(lambda: F.attention_latent_tiled(carried.transpose(0, 1), q_raw, dn, rot, rot, cos, sin, rows, tok_pos, cu_q,
+                                                         slots, d["scale_"], d["window"], mixed.transpose(0, 1), n_seqs, each, splits),
+                       flush=flush, inner=inner)
+        record(f"dasusun latent attention, {label}", ms, n_bytes, flops)
+        x = torch.randn(tokens, w, device=dev)
+        y = torch.randn(tokens, w, device=dev).bfloat16()
+        kept = torch.randn(d["layers"] + 1, tokens, w, device=dev)
+        mix = torch.rand(d["layers"] // 2 + 1, device=dev)
+        ones = torch.ones(w, device=dev)
+        ms = _event_ms(lambda: F.branch_merge(x, y, ones, 1e-6, ones, kept=kept, n_kept=d["layers"] // 2, mix=mix, next_weight=ones,
+                                               next_eps=1e-6, next_dtype=torch.float32), flush=flush, inner=inner)
+        record(f"dasusun branch merge with depth mix of {d['layers'] // 2 + 1} streams and next norm, {label}", ms,
+               tokens * w * (4 + 2 + 4 * (d["layers"] // 2) + 4 + 4 + 4))
+        ms = _event_ms(lambda: F.branch_merge(x, y, ones, 1e-6, ones, next_weight=ones, next_eps=1e-6, next_dtype=torch.bfloat16), flush=flush, inner=inner)
+        record(f"dasusun branch merge with next norm, {label}", ms, tokens * w * (4 + 2 + 4 + 2))
+        state = torch.zeros(n_seqs, 3, w, device=dev)
+        conv_w = torch.randn(w, 4, device=dev)
+        ms = _event_ms(lambda: F.causal_conv(x, conv_w, state, tok_pos, tok_seq, cu_q, slots, torch.bfloat16), flush=flush, inner=inner)
+        record(f"dasusun causal convolution (4 taps), {label}", ms, tokens * w * (4 + 2))
+        proj = torch.randn(tokens, d["q_rank"] + r + rot, device=dev).bfloat16()
+        ms = _event_ms(lambda: F.latent_prepare(proj, d["q_rank"], r, rot, rot, torch.ones(d["q_rank"], device=dev), torch.ones(r, device=dev),
+                                                 1e-6, cos, sin, tok_pos, tok_seq, slots, rows, length - 1), flush=flush, inner=inner)
+        record(f"dasusun latent norms, rotation and cache write, {label}", ms, tokens * (d["q_rank"] + r + rot) * 2 * 2)
+        act = torch.randn(tokens, d["ff"], device=dev).bfloat16()
+        ms = _event_ms(lambda: F.gelu_tanh(act), flush=flush, inner=inner)
+        record(f"dasusun GELU, {label}", ms, tokens * d["ff"] * 4)
+        # ---- the transformer's like kernels
+        hq, hk, hd = t["heads"], t["kv_heads"], t["head_dim"]
+        kv = F.PagedKV(torch.randn(n_seqs * pages_each, hk, 64, hd, device=dev).bfloat16() * 0.1,
+                       torch.randn(n_seqs * pages_each, hk, 64, hd, device=dev).bfloat16() * 0.1, table, F.DecodeWork(dev))
+        q = torch.randn(tokens, hq, hd, device=dev).bfloat16()
+        if n_seqs == 1:
+            ms = _event_ms(lambda: F.attention_prefill(q, kv, cu_q, kv_len, slots, each, hd ** -0.5, 0), flush=flush, inner=inner)
+            record(f"transformer attention, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * length * hk * hd), 4 * hq * hd * tokens * tokens / 2)
+        else:
+            sp = F.decode_splits(n_seqs, hk, length, 64, F.sm_count(dev), F.decode_cluster_places(hd, F.sm_count(dev)))
+            ms = _event_ms(lambda: F.attention_decode(q, kv, kv_len, slots, hd ** -0.5, 0, sp), flush=flush, inner=inner)
+            record(f"transformer attention, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * n_seqs * length * hk * hd), 4 * hq * hd * tokens * length)
+        hs = torch.randn(tokens, t["hidden"], device=dev)
+        delta = torch.randn(tokens, t["hidden"], device=dev).bfloat16()
+        wn = torch.ones(t["hidden"], device=dev)
+        ms = _event_ms(lambda: F.add_rmsnorm(hs, delta, wn, 1e-6, torch.bfloat16), flush=flush, inner=inner)
+        record(f"transformer residual add with next norm, {label}", ms, tokens * t["hidden"] * (4 + 2 + 4 + 2))
+        gu = torch.randn(tokens, 2 * t["ff"], device=dev).bfloat16()
+        ms = _event_ms(lambda: F.swiglu(gu, interleaved=True), flush=flush, inner=inner)
+        record(f"transformer SwiGLU, {label}", ms, tokens * t["ff"] * 6)
+    return out
+
+
+def run_compare(args) -> dict:
+    import gc
+
+    import torch
+
+    from gtar_kimik3_public_b200.ops.library import require_device
+
+    require_device(torch.device("cuda:0"))
+    peak, peak_source = peaks()
+    global PROMPT_LEN
+    results = {}
+    for name, (d, t) in COMPARE_SIZES.items():
+        entry = {}
+        for arch, raw, flops in (("dasusun", _dasusun_config(**d), _dasusun_prefill_flops(d, PREFILL_TOKENS)),
+                                 ("transformer", _transformer_config(**t), _transformer_prefill_flops(t, PREFILL_TOKENS))):
+            model = _device_model(raw)
+            ms = _time_prefill_ms(model, PREFILL_TOKENS)
+            decode = time_decode(model, args.batch, min(args.steps, 64), args.warmup)
+            entry[arch] = {
+                "weight_bytes_per_step": model.weight_bytes_per_step(),
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / (ms / 1e3), 1), "prefill_ms": round(ms, 3),
+                "prefill_frac_of_bf16_peak": round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                "decode_frac_of_hbm_peak": round(decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4),
+                "decode_launches_per_step": decode["launches"] // max(1, min(args.steps, 64)),
+            }
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        d_k = dict(d, scale_=(d["dim"] + d["rot"]) ** -0.5)
+        entry["kernels"] = _kernel_table(d_k, t, peak)
+        results[name] = {"sizes": {"dasusun": d, "transformer": t}, **entry}
+    return {"compare": "dasusun beside transformer at equal layer sizes", "batch": args.batch, "prompt_tokens": PROMPT_LEN,
+            "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16", "data": "synthetic: random token ids, random weights drawn on the device",
+            "peaks": dict(peak, source=peak_source), "l2": "single kernels: a 192 MB buffer is written between the timed calls of the 2,048-token cases; the 8-token cases are 20 calls back to back from a CUDA graph",
+            "results": results}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -573,7 +818,14 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--no-large", action="store_true", help="leave out the points at the 4B and 8B layer sizes")
+    parser.add_argument("--compare", default=None, choices=["dasusun"],
+                        help="instead of the default workload: this architecture beside the transformer at equal layer sizes")
     args = parser.parse_args()
+    if args.compare:
+        if args.warmup < 3:
+            args.warmup = 3
+        print(json.dumps(run_compare(args)))
+        return 0
     if args.impl == "reference":
         if args.warmup < 3:
             args.warmup = 3

@@ -4,7 +4,7 @@
 // (token, head) pairs of one sequence, head running fastest: with sixteen heads a tile is one token, with four heads
 // four consecutive tokens, whose key ranges differ by a few positions only.
 //
-// A block = 16 query rows x 4 warps.  Keys come a page (64 positions) at a time through a two-stage cp.async ring;
+// A block = one, two or four tiles of 16 query rows, four warps a tile.  Keys come a page (64 positions) at a time through a two-stage cp.async ring;
 // rows outside the tile's key range are filled with zeros (a page's unwritten places may hold anything).  Per page:
 //   scores:  warp w forms  S[16 x 16 keys 16w..16w+15]  over the whole row width (rank + rot), masks what its rows
 //            must not see, and posts its rows' maxima;
@@ -28,7 +28,7 @@ namespace {
 
 using namespace attn;
 
-constexpr int WARPS = 4, THREADS = WARPS * 32, ROWS = 16;
+constexpr int COL_WARPS = 4;  // warps that share a 16-row tile: each takes a quarter of a page's keys and of the output's columns
 constexpr int P_STRIDE = PAGE + 8;  // bfloat16 elements: 144 bytes a row, so that ldmatrix rows fall into different banks
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -44,8 +44,11 @@ struct TiledArgs {
     float scale;
 };
 
-template <int NT>  // 8-column tiles of the output a warp owns at most: rank / 32 <= NT
-__global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const TiledArgs a) {
+// NT: 8-column tiles of the output a warp owns at most (rank / 32 <= NT).  MG: 16-row tiles a block holds (1, 2 or 4): its
+// 4 * MG warps share every page it loads, so the rows of MG tiles cost one trip of the page from the L2.
+template <int NT, int MG>
+__global__ void __launch_bounds__(MG * COL_WARPS * 32) attention_latent_tiled_kernel(const TiledArgs a) {
+    constexpr int WARPS = MG * COL_WARPS, THREADS = WARPS * 32, ROWS = MG * 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
@@ -58,9 +61,10 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* k_s = q_s + ROWS * stride;                 // two stages of PAGE rows
     __nv_bfloat16* p_s = k_s + 2 * PAGE * stride;             // [ROWS][P_STRIDE]
-    float* stat_max = reinterpret_cast<float*>(p_s + ROWS * P_STRIDE);  // [2][WARPS][ROWS]
-    float* stat_sum = stat_max + 2 * WARPS * ROWS;                       // [2][WARPS][ROWS]
+    float* stat_max = reinterpret_cast<float*>(p_s + ROWS * P_STRIDE);  // [2][MG][COL_WARPS][16]
+    float* stat_sum = stat_max + 2 * WARPS * 16;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+    const int mg = warp / COL_WARPS, cg = warp % COL_WARPS;  // which 16-row tile, which quarter of keys and columns
 
     // ---- the tile's rows: row r is head (r0 + r) % H of token (r0 + r) / H of the sequence's step
     const int r0 = tile * ROWS;
@@ -72,7 +76,7 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
     int my_pos[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int r = r0 + g + 8 * i;
+        const int r = r0 + mg * 16 + g + 8 * i;
         my_pos[i] = r < n_rows ? a.tok_pos[first_tok + r / a.n_heads] : -1;
     }
     // ---- the pages this block walks
@@ -98,29 +102,38 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
     if (my_first <= my_last) load_page(0, my_first);
     cp_async_commit();
 
-    // ---- stage the query tile: carried part as it is, own part rotated
-    for (int i = tid; i < ROWS * width; i += THREADS) {
-        const int r = i / width, d = i - r * width;
-        const int row = r0 + r;
-        float v = 0.f;
-        if (row < n_rows) {
-            const int t = first_tok + row / a.n_heads, h = row % a.n_heads;
-            if (d < a.rank) {
-                v = __bfloat162float(a.q_carried[(size_t)t * a.qc_tok + (size_t)h * a.qc_head + d]);
-            } else {
-                const int e = d - a.rank;
+    // ---- stage the query tile: the carried part as it is (asynchronous 16-byte copies, zeros for rows beyond the
+    // sequence's last), the own part rotated
+    {
+        const int q_pieces = a.rank / 8;
+        for (int i = tid; i < ROWS * q_pieces; i += THREADS) {
+            const int r = i / q_pieces, piece = i - r * q_pieces;
+            const int row = r0 + r;
+            const bool valid = row < n_rows;
+            const int t = first_tok + (valid ? row / a.n_heads : 0), h = valid ? row % a.n_heads : 0;
+            cp_async_16(q_s + (size_t)r * stride + piece * 8, a.q_carried + (size_t)t * a.qc_tok + (size_t)h * a.qc_head + piece * 8, valid);
+        }
+        cp_async_commit();
+        const int half = a.rot_dims >> 1;
+#pragma unroll 4
+        for (int i = tid; i < ROWS * a.rot; i += THREADS) {
+            const int r = i / a.rot, e = i - r * a.rot;
+            const int row = r0 + r;
+            float v = 0.f;
+            if (row < n_rows) {
+                const int t = first_tok + row / a.n_heads, h = row % a.n_heads;
                 const __nv_bfloat16* own = a.q_raw + ((size_t)t * a.n_heads + h) * a.q_raw_dim + a.q_rot_at;
                 v = __bfloat162float(own[e]);
                 if (e < a.rot_dims) {
-                    const int half = a.rot_dims >> 1, f = e < half ? e : e - half;
+                    const int f = e < half ? e : e - half;
                     const int pos = a.tok_pos[t];
-                    const float c = a.cos_table[(size_t)pos * half + f], s = a.sin_table[(size_t)pos * half + f];
+                    const float c = a.cos_table[(size_t)pos * half + f], sn = a.sin_table[(size_t)pos * half + f];
                     const float other = __bfloat162float(own[e < half ? e + half : e - half]);
-                    v = e < half ? v * c - other * s : v * c + other * s;
+                    v = e < half ? v * c - other * sn : v * c + other * sn;
                 }
             }
+            q_s[(size_t)r * stride + a.rank + e] = __float2bfloat16_rn(v);
         }
-        q_s[(size_t)r * stride + d] = __float2bfloat16_rn(v);
     }
 
     float o[NT][4];
@@ -130,7 +143,7 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
         for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int nt_used = a.rank / 32;          // this warp's 8-column tiles (even: rank is a multiple of 64)
-    const int col0 = warp * (a.rank / 4);     // its first output column
+    const int col0 = cg * (a.rank / 4);       // its first output column
     const float sl2 = a.scale * LOG2E;
     const int k_steps = width / 16;
 
@@ -149,8 +162,8 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
 #pragma unroll
             for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
         {
-            const __nv_bfloat16* q_lane = q_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
-            const __nv_bfloat16* k_lane = kt + (size_t)(warp * 16 + (lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
+            const __nv_bfloat16* q_lane = q_s + (size_t)(mg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
+            const __nv_bfloat16* k_lane = kt + (size_t)(cg * 16 + (lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
             for (int ks = 0; ks < k_steps; ++ks) {
                 uint32_t qa[4], kb[4];
                 ldmatrix_x4(qa, q_lane + ks * 16);
@@ -160,7 +173,7 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
             }
         }
         // ---- mask, and this warp's row maxima
-        const int j_base = pi * PAGE + warp * 16;
+        const int j_base = pi * PAGE + cg * 16;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int n = 0; n < 2; ++n)
@@ -177,11 +190,11 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
         }
-        float* smax = stat_max + stage * WARPS * ROWS;
-        float* ssum = stat_sum + stage * WARPS * ROWS;
+        float* smax = stat_max + (stage * MG + mg) * COL_WARPS * 16;  // [stage][tile][quarter][row]
+        float* ssum = stat_sum + (stage * MG + mg) * COL_WARPS * 16;
         if (tg == 0) {
-            smax[warp * ROWS + g] = mx[0];
-            smax[warp * ROWS + g + 8] = mx[1];
+            smax[cg * 16 + g] = mx[0];
+            smax[cg * 16 + g + 8] = mx[1];
         }
         __syncthreads();
         // ---- the rows' new maxima, probabilities, partial sums; rescale the accumulator
@@ -191,7 +204,7 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
             const int r = g + 8 * i;
             float m = m_run[i];
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) m = fmaxf(m, smax[w * ROWS + r]);
+            for (int w = 0; w < COL_WARPS; ++w) m = fmaxf(m, smax[w * 16 + r]);
             m_new[i] = m;
             corr[i] = m == -INFINITY ? 1.f : exp2f(m_run[i] - m);
             m_run[i] = m;
@@ -206,9 +219,9 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
                 p[c] = m_new[i] == -INFINITY ? 0.f : exp2f(s[n][c] - m_new[i]);
                 sum[i] += p[c];
             }
-            const int col = warp * 16 + n * 8 + 2 * tg;
-            *reinterpret_cast<uint32_t*>(p_s + (size_t)g * P_STRIDE + col) = pack_bf16(p[0], p[1]);
-            *reinterpret_cast<uint32_t*>(p_s + (size_t)(g + 8) * P_STRIDE + col) = pack_bf16(p[2], p[3]);
+            const int col = cg * 16 + n * 8 + 2 * tg;
+            *reinterpret_cast<uint32_t*>(p_s + (size_t)(mg * 16 + g) * P_STRIDE + col) = pack_bf16(p[0], p[1]);
+            *reinterpret_cast<uint32_t*>(p_s + (size_t)(mg * 16 + g + 8) * P_STRIDE + col) = pack_bf16(p[2], p[3]);
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -216,8 +229,8 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
             sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
         }
         if (tg == 0) {
-            ssum[warp * ROWS + g] = sum[0];
-            ssum[warp * ROWS + g + 8] = sum[1];
+            ssum[cg * 16 + g] = sum[0];
+            ssum[cg * 16 + g + 8] = sum[1];
         }
 #pragma unroll
         for (int n = 0; n < NT; ++n)
@@ -231,12 +244,12 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
             const int r = g + 8 * i;
             float t = 0.f;
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) t += ssum[w * ROWS + r];
+            for (int w = 0; w < COL_WARPS; ++w) t += ssum[w * 16 + r];
             l_run[i] = l_run[i] * corr[i] + t;
         }
         // ---- output: P [16 x 64] times this warp's columns of V
         {
-            const __nv_bfloat16* p_lane = p_s + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * P_STRIDE + (lane >> 4) * 8;
+            const __nv_bfloat16* p_lane = p_s + (size_t)(mg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * P_STRIDE + (lane >> 4) * 8;
             const __nv_bfloat16* v_lane = kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + col0 + (lane >> 4) * 8;
 #pragma unroll
             for (int kk = 0; kk < PAGE / 16; ++kk) {
@@ -259,7 +272,7 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
     // ---- results
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int row = r0 + g + 8 * i;
+        const int row = r0 + mg * 16 + g + 8 * i;
         if (row >= n_rows) continue;
         const int t = first_tok + row / a.n_heads, h = row % a.n_heads;
         if (a.splits == 1) {
@@ -275,7 +288,7 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
 #pragma unroll
             for (int n = 0; n < NT; ++n)
                 if (n < nt_used) *reinterpret_cast<float2*>(dst + n * 8 + 2 * tg) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
-            if (warp == 0 && tg == 0) {
+            if (cg == 0 && tg == 0) {
                 a.part_ml[grow * 2] = m_run[i];
                 a.part_ml[grow * 2 + 1] = l_run[i];
             }
@@ -283,51 +296,69 @@ __global__ void __launch_bounds__(THREADS) attention_latent_tiled_kernel(const T
     }
 }
 
-// One warp per (token, head): the splits' partial results in split order.  Maxima are in the exponent-of-two scale
-// of the kernel above.
-__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, long long out_tok, long long out_head, int n_rows_total,
-                                    int n_heads, int rank, int splits) {
+// One thread per (token, head, output column): the splits' partial results in split order.  Every thread forms its
+// row's weights itself (the statistics are a few numbers, the same for a whole warp), so that none of its loads waits
+// for another.  Maxima are in the exponent-of-two scale of the kernel above.
+constexpr int MAX_SPLITS = 16;
+
+__global__ void __launch_bounds__(256) latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                           __nv_bfloat16* __restrict__ out, long long out_tok, long long out_head,
+                                                           int n_rows_total, int n_heads, int rank, int splits) {
     pdl_launch_dependents();
     pdl_wait();
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= n_rows_total) return;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_rows_total * rank) return;
+    const int row = (int)(idx / rank), d = (int)(idx - (long long)row * rank);
+    float ms[MAX_SPLITS], ls[MAX_SPLITS], os[MAX_SPLITS];
+    const size_t step = (size_t)n_rows_total * rank;
+#pragma unroll
+    for (int s = 0; s < MAX_SPLITS; ++s) {
+        const bool on = s < splits;
+        ms[s] = on ? part_ml[((size_t)s * n_rows_total + row) * 2] : -INFINITY;
+        ls[s] = on ? part_ml[((size_t)s * n_rows_total + row) * 2 + 1] : 0.f;
+        os[s] = on ? part_o[s * step + idx] : 0.f;  // a split that saw nothing left zeros
+    }
     float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((size_t)s * n_rows_total + row) * 2]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[((size_t)s * n_rows_total + row) * 2];
-        if (ms != -INFINITY) l += part_ml[((size_t)s * n_rows_total + row) * 2 + 1] * exp2f(ms - m);
+#pragma unroll
+    for (int s = 0; s < MAX_SPLITS; ++s) m = fmaxf(m, ms[s]);
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAX_SPLITS; ++s) {
+        const float w = ms[s] == -INFINITY ? 0.f : exp2f(ms[s] - m);
+        l = fmaf(ls[s], w, l);
+        acc = fmaf(os[s], w, acc);
     }
     const int t = row / n_heads, h = row % n_heads;
-    __nv_bfloat16* dst = out + (size_t)t * out_tok + (size_t)h * out_head;
-    for (int d = lane; d < rank; d += 32) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[((size_t)s * n_rows_total + row) * 2];
-            if (ms != -INFINITY) acc += part_o[((size_t)s * n_rows_total + row) * rank + d] * exp2f(ms - m);
-        }
-        dst[d] = __float2bfloat16_rn(acc / l);
+    out[(size_t)t * out_tok + (size_t)h * out_head + d] = __float2bfloat16_rn(acc / l);
+}
+
+size_t tiled_smem(int width, int mg) {
+    return (size_t)(mg * 16 + 2 * PAGE) * (width + 8) * 2 + (size_t)mg * 16 * P_STRIDE * 2 + 4 * (size_t)mg * COL_WARPS * 16 * 4;
+}
+
+template <int NT, int MG>
+void launch_tiled(const TiledArgs& a, unsigned tiles16, unsigned n_seqs, int width, cudaStream_t s) {
+    static bool prepared = false;
+    if (!prepared) {
+        cudaFuncSetAttribute(attention_latent_tiled_kernel<NT, MG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        prepared = true;
     }
+    gk_launch(attention_latent_tiled_kernel<NT, MG>, dim3((tiles16 + MG - 1) / MG, n_seqs, (unsigned)a.splits), dim3(MG * COL_WARPS * 32),
+              tiled_smem(width, MG), s, a);
 }
 
 template <int NT>
-int launch_tiled(const TiledArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
-    static bool prepared = false;
-    if (!prepared) {
-        cudaFuncSetAttribute(attention_latent_tiled_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        prepared = true;
-    }
-    gk_launch(attention_latent_tiled_kernel<NT>, grid, dim3(THREADS), smem, s, a);
-    return 0;
+void launch_tiled_rows(const TiledArgs& a, unsigned tiles16, unsigned n_seqs, int width, cudaStream_t s) {
+    // as many 16-row tiles a block as a sequence brings (up to four) and as fit in shared memory beside two pages
+    if (tiles16 >= 4 && tiled_smem(width, 4) <= 200 * 1024) launch_tiled<NT, 4>(a, tiles16, n_seqs, width, s);
+    else if (tiles16 >= 2 && tiled_smem(width, 2) <= 200 * 1024) launch_tiled<NT, 2>(a, tiles16, n_seqs, width, s);
+    else launch_tiled<NT, 1>(a, tiles16, n_seqs, width, s);
 }
 
 }  // namespace
 
-// Shared memory the kernel needs for rows of `width` = rank + rot.
-GK_EXPORT int gk_attention_latent_tiled_smem(int width) {
-    return (ROWS + 2 * PAGE) * (width + 8) * 2 + ROWS * P_STRIDE * 2 + 4 * WARPS * ROWS * 4;
-}
+// Shared memory the kernel needs at least (one 16-row tile a block) for rows of `width` = rank + rot.
+GK_EXPORT int gk_attention_latent_tiled_smem(int width) { return (int)tiled_smem(width, 1); }
 
 GK_EXPORT int gk_attention_latent_tiled(const void* q_carried, long long qc_tok, long long qc_head, const void* q_raw,
                                         int q_raw_dim, int q_rot_at, const float* cos_table, const float* sin_table,
@@ -342,14 +373,15 @@ GK_EXPORT int gk_attention_latent_tiled(const void* q_carried, long long qc_tok,
     GK_REQUIRE(rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0, "attention_latent_tiled: bad rotation sizes");
     GK_REQUIRE(q_rot_at >= 0 && q_rot_at + rot <= q_raw_dim, "attention_latent_tiled: the rotated part lies outside the head");
     GK_REQUIRE(page_size == PAGE, "attention_latent_tiled: pages must hold %d positions", PAGE);
-    GK_REQUIRE(window >= 0 && splits >= 1 && splits <= 65535, "attention_latent_tiled: bad window or splits");
+    GK_REQUIRE(window >= 0 && splits >= 1 && splits <= MAX_SPLITS, "attention_latent_tiled: bad window, or more than %d splits", MAX_SPLITS);
     GK_REQUIRE(splits == 1 || (part_o && part_ml), "attention_latent_tiled: splits need scratch");
     GK_REQUIRE(((uintptr_t)pages & 15) == 0 && ((uintptr_t)out & 3) == 0 && out_tok % 2 == 0 && out_head % 2 == 0,
                "attention_latent_tiled: misaligned pages or output");
+    GK_REQUIRE(((uintptr_t)q_carried & 15) == 0 && qc_tok % 8 == 0 && qc_head % 8 == 0,
+               "attention_latent_tiled: the carried queries' rows must start at 16-byte boundaries");
     if (n_tokens == 0) return GK_OK;
-    const size_t smem = (size_t)gk_attention_latent_tiled_smem(rank + rot);
-    GK_REQUIRE(smem <= 200 * 1024, "attention_latent_tiled: rows of %d do not fit in shared memory", rank + rot);
-    const long long tiles = ((long long)max_q_len * n_heads + ROWS - 1) / ROWS;
+    GK_REQUIRE(tiled_smem(rank + rot, 1) <= 200 * 1024, "attention_latent_tiled: rows of %d do not fit in shared memory", rank + rot);
+    const long long tiles = ((long long)max_q_len * n_heads + 15) / 16;
     GK_REQUIRE(tiles <= 2147483647LL && n_seqs <= 65535, "attention_latent_tiled: too many tiles or sequences");
     TiledArgs a;
     a.q_carried = (const __nv_bfloat16*)q_carried; a.qc_tok = qc_tok; a.qc_head = qc_head;
@@ -359,17 +391,17 @@ GK_EXPORT int gk_attention_latent_tiled(const void* q_carried, long long qc_tok,
     a.tok_pos = tok_pos; a.cu_q = cu_q; a.slots = slots; a.block_table = block_table;
     a.n_heads = n_heads; a.rank = rank; a.rot = rot; a.rot_dims = rot_dims; a.max_pages = max_pages; a.splits = splits;
     a.n_rows_total = n_tokens * n_heads; a.window = window; a.scale = scale;
-    dim3 grid((unsigned)tiles, (unsigned)n_seqs, (unsigned)splits);
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = rank / 32;
-    if (nt <= 2) launch_tiled<2>(a, grid, smem, s);
-    else if (nt <= 4) launch_tiled<4>(a, grid, smem, s);
-    else if (nt <= 8) launch_tiled<8>(a, grid, smem, s);
-    else launch_tiled<16>(a, grid, smem, s);
+    if (nt <= 2) launch_tiled_rows<2>(a, (unsigned)tiles, (unsigned)n_seqs, rank + rot, s);
+    else if (nt <= 4) launch_tiled_rows<4>(a, (unsigned)tiles, (unsigned)n_seqs, rank + rot, s);
+    else if (nt <= 8) launch_tiled_rows<8>(a, (unsigned)tiles, (unsigned)n_seqs, rank + rot, s);
+    else launch_tiled_rows<16>(a, (unsigned)tiles, (unsigned)n_seqs, rank + rot, s);
     GK_CHECK_LAUNCH("attention_latent_tiled");
     if (splits > 1) {
         const int rows = n_tokens * n_heads;
-        gk_launch(latent_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, (const float*)part_o, (const float*)part_ml,
+        const long long cells = (long long)rows * rank;
+        gk_launch(latent_merge_kernel, dim3((unsigned)((cells + 255) / 256)), dim3(256), 0, s, (const float*)part_o, (const float*)part_ml,
                   (__nv_bfloat16*)out, out_tok, out_head, rows, n_heads, rank, splits);
         GK_CHECK_LAUNCH("latent_merge");
     }
