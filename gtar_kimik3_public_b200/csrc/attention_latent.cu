@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(PREP_THREADS) latent_prepare_kernel(
 }
 
 constexpr int WARPS = 4;
-constexpr int MAX_ACC = 16;  // rank <= 512
+constexpr int MAX_ACC = 32;  // rank <= 1024
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int d);

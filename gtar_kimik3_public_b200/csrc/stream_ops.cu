@@ -59,11 +59,13 @@ __global__ void __launch_bounds__(ROW_THREADS) branch_merge_kernel(
 
 // One thread per (token, channel).  `a` holds the step's inputs, `state` [n_slots, taps - 1, width] the inputs of
 // before: entry k of a sequence's state is its input at position  past - (taps - 1) + k.
+// `update` (only where every sequence of the step brings ONE token, so that this thread alone reads and writes its
+// sequence's entries for the channel): the state is moved on by the token here and no second kernel is needed.
 template <typename TO>
-__global__ void causal_conv_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ state,
+__global__ void causal_conv_kernel(const float* __restrict__ a, const float* __restrict__ w, float* state,
                                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                    const int* __restrict__ cu_q, const int* __restrict__ slots, TO* __restrict__ out,
-                                   int n_tokens, int width, int taps) {
+                                   int n_tokens, int width, int taps, int update) {
     pdl_launch_dependents();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -84,6 +86,11 @@ __global__ void causal_conv_kernel(const float* __restrict__ a, const float* __r
         acc = fmaf(w[(size_t)c * taps + j], v, acc);
     }
     out[idx] = from_float<TO>(own + acc);
+    if (update && taps > 1) {
+        float* mine = state + (size_t)slots[seq] * (taps - 1) * width + c;
+        for (int k = 0; k + 1 < taps - 1; ++k) mine[(size_t)k * width] = mine[(size_t)(k + 1) * width];
+        mine[(size_t)(taps - 2) * width] = own;
+    }
 }
 
 // One thread per (sequence, channel): entry k of the new state is the input at position  new_len - (taps - 1) + k,
@@ -146,9 +153,9 @@ GK_EXPORT int gk_branch_merge(const float* x, const void* y, int y_dtype, const 
     return GK_OK;
 }
 
-GK_EXPORT int gk_causal_conv(const float* a, const float* w, const float* state, const int* tok_pos, const int* tok_seq,
+GK_EXPORT int gk_causal_conv(const float* a, const float* w, float* state, const int* tok_pos, const int* tok_seq,
                              const int* cu_q, const int* slots, void* out, int out_dtype, int n_tokens, int width, int taps,
-                             void* stream) {
+                             int update_single_token_state, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "causal_conv: bad dtype code");
     GK_REQUIRE(n_tokens >= 0 && width > 0 && taps >= 1, "causal_conv: bad sizes");
     GK_REQUIRE(taps == 1 || state != nullptr, "causal_conv: more than one tap needs a state");
@@ -159,7 +166,7 @@ GK_EXPORT int gk_causal_conv(const float* a, const float* w, const float* state,
     GK_REQUIRE(blocks < 2147483647LL, "causal_conv: too many elements");
     GK_DISPATCH_DTYPE(out_dtype, TO, {
         gk_launch(causal_conv_kernel<TO>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, a, w, state, tok_pos,
-                  tok_seq, cu_q, slots, (TO*)out, n_tokens, width, taps);
+                  tok_seq, cu_q, slots, (TO*)out, n_tokens, width, taps, update_single_token_state);
     })
     GK_CHECK_LAUNCH("causal_conv");
     return GK_OK;

@@ -1076,9 +1076,11 @@ def branch_merge(x: torch.Tensor, y: torch.Tensor, norm_weight: torch.Tensor, ep
 
 
 def causal_conv(a: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
-                cu_q: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+                cu_q: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype, update_single_token_state: bool = False) -> torch.Tensor:
     """``a + conv(a)`` over time on each channel: ``a [n_tokens, width]`` 32-bit, ``weight [width, taps]`` 32-bit,
-    ``state [n_slots, taps - 1, width]`` the sequences' inputs of before (read only; see ``conv_state``)."""
+    ``state [n_slots, taps - 1, width]`` the sequences' inputs of before (read only; ``conv_state`` brings it up to date
+    afterwards).  ``update_single_token_state``: every sequence of the step brings exactly one token, and the kernel moves
+    the states on itself."""
     require_device(a.device)
     _check(a, "a", torch.float32, 2)
     _check(weight, "weight", torch.float32, 2)
@@ -1092,7 +1094,7 @@ def causal_conv(a: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | Non
             raise KernelError(f"state {tuple(state.shape)} does not hold {taps - 1} inputs of width {width}")
     out = torch.empty((n, width), dtype=out_dtype, device=a.device)
     call("gk_causal_conv", ptr(a), ptr(weight), ptr(state) if taps > 1 else None, ptr(tok_pos), ptr(tok_seq), ptr(cu_q),
-         ptr(slots), ptr(out), dtype_code(out_dtype), n, width, taps, stream_ptr())
+         ptr(slots), ptr(out), dtype_code(out_dtype), n, width, taps, int(bool(update_single_token_state)), stream_ptr())
     return out
 
 

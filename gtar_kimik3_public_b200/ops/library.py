@@ -38,7 +38,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_gemm_f32": [P, I, P, P, I, I, I, I, L, L, L, P],
     "gk_gemm_f32_batched": [P, I, P, P, I, I, I, I, I, L, L, L, L, L, L, P],
     "gk_branch_merge": [P, P, I, P, P, F, P, L, I, P, P, P, F, P, I, I, I, P],
-    "gk_causal_conv": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "gk_causal_conv": [P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "gk_conv_state": [P, P, P, P, I, I, I, P],
     "gk_gelu_tanh": [P, P, I, L, P],
     "gk_latent_prepare": [P, I, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],

@@ -185,8 +185,11 @@ class SandwichBlock(Block):
         if a is None:
             a = self.norm_in.forward(h, None, self.input_dtype(ctx))
         if self.conv_taps:
-            g = F.causal_conv(a, self.conv, state, ctx.tok_pos, ctx.tok_seq, ctx.cu_q, ctx.slots, ctx.dtype)
-            if state is not None and not ctx.extras.get("cache_read_only", False):
+            keep = state is not None and not ctx.extras.get("cache_read_only", False)
+            # one token a sequence: the convolution's kernel moves the states on itself
+            g = F.causal_conv(a, self.conv, state, ctx.tok_pos, ctx.tok_seq, ctx.cu_q, ctx.slots, ctx.dtype,
+                              update_single_token_state=keep and ctx.all_single)
+            if keep and not ctx.all_single:
                 F.conv_state(a, state, ctx.cu_q, ctx.slots, ctx.n_seqs)
         else:
             g = a

@@ -194,3 +194,27 @@ def test_trace_replay_from_the_command_line(tag, dtype, tmp_path):
         das_check(tag, dtype, a, [70 + i], rows[:1], f"trace step {i + 1}, request a")
         if i < 2:
             das_check(tag, dtype, b, [18 + i], rows[1:], f"trace step {i + 1}, request b")
+
+
+def test_command_line_generates_the_greedy_tokens():
+    """The generation command line loads the folder by its config.json and prints the plain implementation's greedy tokens."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    (prompt,) = das_requests("das_a", [9], seed=13)
+    run = subprocess.run(
+        [sys.executable, "-m", "gtar_kimik3_public_b200.scripts.generate", "--model", str(das_folder("das_a")), "--dtype", "float32",
+         "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--temperature", "0"],
+        capture_output=True, text=True, cwd=root, timeout=300)
+    assert run.returncode == 0, run.stderr[-2000:]
+    produced = [int(t) for t in run.stdout.strip().splitlines()[0].split(",")]
+    assert len(produced) == 6
+    sequence = list(prompt)
+    for token in produced:
+        logits = das_plain_logits("das_a", sequence, "f64")[-1]
+        top = torch.topk(logits, 2).values
+        if (top[0] - top[1]).item() > 1e-3:
+            assert int(logits.argmax()) == token
+        sequence.append(token)
