@@ -71,6 +71,8 @@ __device__ __forceinline__ void copy16_async(void* smem_dst, const void* src, in
 }
 
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+// the tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 
 // ROW_SETS: sets of eight tokens, 1, 2 or 4.  An MMA takes two sets on its rows 0..7 and 8..15 (with one set the
 // upper rows are zero); with four sets (17 to 32 tokens) every weight piece goes through two MMAs' worth of
@@ -165,14 +167,18 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
         for (int half = 0; half < (TWO_ROWS ? 2 : 1); ++half) {
             const int token = 16 * tile + group + 8 * half;
             if (token >= p.tokens) continue;
-            const float a = sum[2 * half], b = sum[2 * half + 1];
+            float a = sum[2 * half], b = sum[2 * half + 1];
+            if (p.swiglu == 2) {  // an activation of one number: applied where the sums are, then stored as any result
+                a = gelu_tanh(a);
+                b = gelu_tanh(b);
+            }
             if (p.resid) {
                 float* o = p.resid + (size_t)token * p.ldr + col;
                 const float na = old[tile][half].x + __bfloat162float(__float2bfloat16(a));
                 const float nb = old[tile][half].y + __bfloat162float(__float2bfloat16(b));
                 if (col + 1 < p.n) *reinterpret_cast<float2*>(o) = make_float2(na, nb);
                 else if (col < p.n) o[0] = na;
-            } else if (p.swiglu) {
+            } else if (p.swiglu == 1) {
                 if (col + 1 < p.n)
                     reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)token * p.ldo + (col >> 1)] = __float2bfloat16(silu(a) * b);
             } else if (p.out_f32) {
@@ -496,8 +502,8 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
 }  // namespace
 
 // OUT[t, :] = x[t, :] @ w^T for 1 to 16 tokens (17 to 32 where 257 <= k <= 1024) and up to 64 weight rows per SM; `w` [n, k] and `x` [tokens, k]
-// bfloat16 with rows in steps of 8 elements (16 bytes); OUT bfloat16 or float32, [tokens, n], or with `swiglu`
-// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows.
+// bfloat16 with rows in steps of 8 elements (16 bytes); OUT bfloat16 or float32, [tokens, n], or with `swiglu` = 1
+// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows; `swiglu` = 2 stores gelu_tanh of every result.
 GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const void* x, int tokens, long long ldx, void* out,
                            int out_dtype, int swiglu, void* stream) {
     GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 32, "gemv: takes 1 to 32 tokens and positive sizes; got %d tokens, n=%d k=%d",
@@ -506,7 +512,8 @@ GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const voi
                k, ldw, ldx);
     GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 3) == 0, "gemv: operands must be 16-byte aligned");
     GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemv: bad output dtype");
-    GK_REQUIRE(!swiglu || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");
+    GK_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemv: output stage %d is none of store, SwiGLU, GELU", swiglu);
+    GK_REQUIRE(swiglu != 1 || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");
     GemvParams p = {};
     p.w = (const __nv_bfloat16*)w;
     p.x = (const __nv_bfloat16*)x;
@@ -516,7 +523,7 @@ GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const voi
     p.tokens = tokens;
     p.ldw = ldw;
     p.ldx = ldx;
-    p.ldo = swiglu ? n / 2 : n;
+    p.ldo = swiglu == 1 ? n / 2 : n;
     p.out_f32 = out_dtype == GK_F32;
     p.swiglu = swiglu;
     return launch_gemv(p, (cudaStream_t)stream);
@@ -536,6 +543,7 @@ GK_EXPORT int gk_gemv_bf16_stream(const void* w, int n, int k, long long ldw, co
     GK_REQUIRE(norm_h != nullptr || (x != nullptr && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0), "gemv: activations must be 16-byte aligned rows");
     GK_REQUIRE(norm_h == nullptr || (norm_w != nullptr && ldh % 4 == 0 && ((uintptr_t)norm_h & 15) == 0 && ((uintptr_t)norm_w & 15) == 0 && norm_eps > 0.f),
                "gemv: the norm on load needs 16-byte aligned rows and weights and a positive eps");
+    GK_REQUIRE(swiglu == 0 || swiglu == 1, "gemv: the stream forms take the store and SwiGLU output stages");
     GK_REQUIRE(resid == nullptr || (!swiglu && ldr % 2 == 0 && ((uintptr_t)resid & 7) == 0), "gemv: the residual output stage needs 8-byte aligned rows and no SwiGLU");
     GK_REQUIRE(resid != nullptr || (out != nullptr && GK_VALID_DTYPE(out_dtype) && ((uintptr_t)out & 3) == 0), "gemv: bad output");
     GK_REQUIRE(!swiglu || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");

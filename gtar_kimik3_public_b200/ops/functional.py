@@ -428,10 +428,11 @@ def gemv_suits(m: int, n: int, k: int, device: torch.device) -> bool:
 
 
 def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
-         out: torch.Tensor | None = None) -> torch.Tensor:
+         out: torch.Tensor | None = None, gelu: bool = False) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` for up to 16 tokens (32 where ``gemv_suits`` says so): weights go from memory straight into registers and
     through ``mma.sync`` with 32-bit accumulation; made for the latency of a decode step, where a projection
-    is a few megabytes of weights and next to no arithmetic.  ``swiglu`` as in ``gemm_tc``."""
+    is a few megabytes of weights and next to no arithmetic.  ``swiglu`` as in ``gemm_tc``; ``gelu`` stores the tanh form
+    of GELU of every result (the 32-bit sums go through it before they are rounded)."""
     require_device(x.device)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
@@ -443,13 +444,15 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.b
         raise KernelError(f"gemv takes up to {GEMV_MAX_TOKENS_SHORT_K} tokens, got {m}")
     if swiglu and n % 2:
         raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
+    if swiglu and gelu:
+        raise KernelError("one output stage at a time: SwiGLU or GELU")
     n_out = n // 2 if swiglu else n
     if out is None:
         out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
     _check(out, "out", out_dtype, 2)
     if tuple(out.shape) != (m, n_out):
         raise KernelError(f"out has shape {tuple(out.shape)}, expected {(m, n_out)}")
-    call("gk_gemv_bf16", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype), int(swiglu), stream_ptr())
+    call("gk_gemv_bf16", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype), 2 if gelu else int(swiglu), stream_ptr())
     return out
 
 

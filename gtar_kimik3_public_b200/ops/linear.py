@@ -29,14 +29,22 @@ def _tc_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           swiglu: bool = False) -> torch.Tensor:
+           swiglu: bool = False, gelu: bool = False) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T -> [M, N]`` in ``out_dtype`` (default: ``x.dtype``).
 
     ``swiglu``: ``weight`` holds gate and up rows alternately and the result is ``silu(gate) * up``
-    of width ``N / 2``.
+    of width ``N / 2``.  ``gelu``: the tanh form of GELU of the result; where the few-token product runs it is that
+    kernel's output stage (applied to the 32-bit sums), elsewhere a kernel of its own behind the product.
     """
     require_device(x.device)
     out_dtype = out_dtype or x.dtype
+    if gelu:
+        if swiglu:
+            raise KernelError("one activation at a time: SwiGLU or GELU")
+        if (weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and _tc_ok(x, weight)
+                and F.gemv_suits(x.shape[0], weight.shape[0], x.shape[1], x.device)):
+            return F.gemv(x, weight, out_dtype, gelu=True)
+        return F.gelu_tanh(linear(x, weight, out_dtype))
     if weight.dtype == torch.float32:
         y = F.linear_f32(x, weight, torch.float32 if swiglu else out_dtype)
         return F.swiglu(y, interleaved=True).to(out_dtype) if swiglu else y

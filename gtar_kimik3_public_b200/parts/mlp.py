@@ -81,7 +81,7 @@ class GeluFeedForward(FeedForward):
         return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
 
     def forward(self, x, ctx: StepContext) -> torch.Tensor:
-        return linear(F.gelu_tanh(linear(x, self.w_up)), self.w_down)
+        return linear(linear(x, self.w_up, gelu=True), self.w_down)
 
 
 register_part("feed_forward", "gelu", GeluFeedForward)

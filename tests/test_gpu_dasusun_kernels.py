@@ -100,6 +100,21 @@ def test_gelu():
     assert torch.allclose(got, plain.gelu_tanh(z.bfloat16().double()), atol=0.04, rtol=0.01)
 
 
+@pytest.mark.parametrize("tokens", [1, 5, 16])
+def test_gelu_in_the_few_token_product(tokens):
+    """Few tokens: GELU is the product's output stage; the result is GELU of the 32-bit sums, rounded once."""
+    from gtar_kimik3_public_b200.ops.linear import linear
+
+    gen = torch.Generator().manual_seed(tokens)
+    x = torch.randn(tokens, 256, generator=gen).bfloat16()
+    w = (torch.randn(200, 256, generator=gen) * 0.2).bfloat16()
+    got = linear(x.to(DEV), w.to(DEV), gelu=True).cpu().double()
+    want = plain.gelu_tanh(x.double() @ w.double().T)
+    assert got.shape == (tokens, 200)
+    assert torch.allclose(got, want, atol=0.03, rtol=0.01)
+    assert not torch.allclose(got, x.double() @ w.double().T, atol=0.03, rtol=0.01)  # the activation was applied
+
+
 @pytest.mark.parametrize("dims,base,scaling", [
     (16, 250000.0, {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
     (8, 10000.0, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}),
