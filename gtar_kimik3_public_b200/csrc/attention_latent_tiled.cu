@@ -22,6 +22,8 @@
 // tile is staged (32-bit, tables of cos and sin).  Sizes: rank a multiple of 64 up to 512, rot a multiple of 16,
 // pages of 64 positions.
 
+#include <stdlib.h>
+
 #include "attention_mma.cuh"
 
 namespace {
@@ -52,7 +54,8 @@ __global__ void __launch_bounds__(MG * COL_WARPS * 32) attention_latent_tiled_ke
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
-    const int seq = blockIdx.y, tile = blockIdx.x, split = blockIdx.z;
+    // the SMs take blocks in index order and a sequence's last tiles have the most keys: those go first
+    const int seq = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x, split = blockIdx.z;
     const int first_tok = a.cu_q[seq], n_tok = a.cu_q[seq + 1] - first_tok;
     const int n_rows = n_tok * a.n_heads;
     if (tile * ROWS >= n_rows) return;
@@ -375,6 +378,9 @@ void launch_tiled(const TiledArgs& a, unsigned tiles16, unsigned n_seqs, int wid
 template <int NT>
 void launch_tiled_rows(const TiledArgs& a, unsigned tiles16, unsigned n_seqs, int width, cudaStream_t s) {
     // as many 16-row tiles a block as a sequence brings (up to four) and as fit in shared memory beside two pages
+    static const int forced = getenv("GTAR_B200_LATENT_ROW_TILES") ? atoi(getenv("GTAR_B200_LATENT_ROW_TILES")) : 0;  // for measurements
+    if (forced == 1) { launch_tiled<NT, 1>(a, tiles16, n_seqs, width, s); return; }
+    if (forced == 2 && tiled_smem(width, 2) <= 200 * 1024) { launch_tiled<NT, 2>(a, tiles16, n_seqs, width, s); return; }
     if (tiles16 >= 4 && tiled_smem(width, 4) <= 200 * 1024) launch_tiled<NT, 4>(a, tiles16, n_seqs, width, s);
     else if (tiles16 >= 2 && tiled_smem(width, 2) <= 200 * 1024) launch_tiled<NT, 2>(a, tiles16, n_seqs, width, s);
     else launch_tiled<NT, 1>(a, tiles16, n_seqs, width, s);
