@@ -38,7 +38,7 @@ DAS_A = {
 DAS_B = {
     "architecture": "Dasusun", "vocab": 200, "width": 72, "norm": {"eps": 1e-6}, "canon": {"taps": 2},
     "layers": [
-        _layer(_mixer(4, 8, 24, 16, 40, 24, 64, 24, 250000.0, _SCALING_B), 96),
+        _layer(_mixer(4, 8, 24, 16, 40, 24, 64, 24, 150000.0, _SCALING_B), 96),
         _layer(_mixer(2, 40, 8, 24, 16, 48, 65, 4, 100.0, None), 200),
         _layer(_mixer(2, 16, 8, 16, 32, 32, 1, 8, 10000.0, None), None),
         _layer(_mixer(5, 8, 8, 8, 56, 16, 200, 8, 10000.0, _SCALING_B), 64),
@@ -58,7 +58,7 @@ DAS_D["layers"] = DAS_D["layers"][:2]
 DAS_E = {
     "architecture": "Dasusun", "vocab": 256, "width": 128, "norm": {"eps": 1e-6}, "canon": {"taps": 3},
     "layers": [
-        _layer(_mixer(3, 16, 16, 24, 64, 64, 40, 16, 250000.0, _SCALING_B), 256),
+        _layer(_mixer(3, 16, 16, 24, 64, 64, 44, 16, 300000.0, _SCALING_B), 256),
         _layer(_mixer(20, 8, 32, 8, 32, 128, 130, 16, 10000.0, None), 128),
         _layer(_mixer(5, 24, 16, 16, 48, 64, None, 16, 10000.0, _SCALING_A), None),
         _layer(_mixer(16, 16, 16, 16, 64, 64, 64, 8, 1000.0, None), 192),

@@ -88,7 +88,7 @@ def test_layers_with_the_same_rotation_share_tables():
 
 
 @pytest.mark.parametrize("dims,base,scaling", [
-    (16, 250000.0, {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
+    (16, 200000.0, {"factor": 3.0, "original": 1024, "fast": 20.0, "slow": 1.5}),
     (8, 10000.0, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}),
     (24, 100.0, {"factor": 1.5, "original": 256, "fast": 24.0, "slow": 0.5}),
 ])
