@@ -91,15 +91,23 @@ __global__ void __launch_bounds__(MG * COL_WARPS * 32) attention_latent_tiled_ke
     const int* table = a.block_table + (size_t)a.slots[seq] * a.max_pages;
     const int pieces = width / 8;  // 16-byte pieces of a row
 
+    // a thread's pieces of a page lie THREADS apart: row and piece of the first, and what one step adds (no division in the loop)
+    const int lp_row0 = tid / pieces, lp_piece0 = tid - lp_row0 * pieces;
+    const int lp_row_step = THREADS / pieces, lp_piece_step = THREADS - lp_row_step * pieces;
     auto load_page = [&](int stage, int page_index) {
         const int page = table[page_index];
         const __nv_bfloat16* src = a.pages + (size_t)page * PAGE * width;
         __nv_bfloat16* dst = k_s + (size_t)stage * PAGE * stride;
-        const int j0 = page_index * PAGE;
-        for (int i = tid; i < PAGE * pieces; i += THREADS) {
-            const int row = i / pieces, piece = i - row * pieces;
-            const int j = j0 + row;
-            cp_async_16(dst + (size_t)row * stride + piece * 8, src + (size_t)row * width + piece * 8, j >= key_lo && j <= pos_hi);
+        const int row_lo = key_lo - page_index * PAGE, row_hi = pos_hi - page_index * PAGE;  // rows of the page inside the key range
+        int row = lp_row0, piece = lp_piece0;
+        while (row < PAGE) {
+            cp_async_16(dst + row * stride + piece * 8, src + row * width + piece * 8, row >= row_lo && row <= row_hi);
+            row += lp_row_step;
+            piece += lp_piece_step;
+            if (piece >= pieces) {
+                piece -= pieces;
+                ++row;
+            }
         }
     };
     if (my_first <= my_last) load_page(0, my_first);
@@ -165,23 +173,24 @@ __global__ void __launch_bounds__(MG * COL_WARPS * 32) attention_latent_tiled_ke
 #pragma unroll
             for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
         {
-            const __nv_bfloat16* q_lane = q_s + (size_t)(mg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
-            const __nv_bfloat16* k_lane = kt + (size_t)(cg * 16 + (lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
+            // 32-bit shared-memory addresses, advanced by 32 bytes a step (no conversion of a generic pointer per ldmatrix)
+            const uint32_t q_at = smem_u32(q_s + (size_t)(mg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8);
+            const uint32_t k_at = smem_u32(kt + (size_t)(cg * 16 + (lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8);
             if constexpr (NT <= 8) {
                 // the fragments of the next step are asked for before the products of this one are issued (measured: 4% off
                 // the kernel at a latent of 256; at 512, where the accumulator leaves few registers, 7% slower, so not there)
                 uint32_t qa0[4], kb0[4], qa1[4], kb1[4];
-                ldmatrix_x4(qa0, q_lane);
-                ldmatrix_x4(kb0, k_lane);
+                ldmatrix_x4_at(qa0, q_at);
+                ldmatrix_x4_at(kb0, k_at);
                 int ks = 0;
                 for (; ks + 2 <= k_steps; ks += 2) {
-                    ldmatrix_x4(qa1, q_lane + (ks + 1) * 16);
-                    ldmatrix_x4(kb1, k_lane + (ks + 1) * 16);
+                    ldmatrix_x4_at(qa1, q_at + (ks + 1) * 32);
+                    ldmatrix_x4_at(kb1, k_at + (ks + 1) * 32);
                     mma_16816(s[0], qa0, kb0[0], kb0[1]);
                     mma_16816(s[1], qa0, kb0[2], kb0[3]);
                     if (ks + 2 < k_steps) {
-                        ldmatrix_x4(qa0, q_lane + (ks + 2) * 16);
-                        ldmatrix_x4(kb0, k_lane + (ks + 2) * 16);
+                        ldmatrix_x4_at(qa0, q_at + (ks + 2) * 32);
+                        ldmatrix_x4_at(kb0, k_at + (ks + 2) * 32);
                     }
                     mma_16816(s[0], qa1, kb1[0], kb1[1]);
                     mma_16816(s[1], qa1, kb1[2], kb1[3]);
@@ -193,8 +202,8 @@ __global__ void __launch_bounds__(MG * COL_WARPS * 32) attention_latent_tiled_ke
             } else {
                 for (int ks = 0; ks < k_steps; ++ks) {
                     uint32_t qa[4], kb[4];
-                    ldmatrix_x4(qa, q_lane + ks * 16);
-                    ldmatrix_x4(kb, k_lane + ks * 16);
+                    ldmatrix_x4_at(qa, q_at + ks * 32);
+                    ldmatrix_x4_at(kb, k_at + ks * 32);
                     mma_16816(s[0], qa, kb[0], kb[1]);
                     mma_16816(s[1], qa, kb[2], kb[3]);
                 }
@@ -277,17 +286,18 @@ __global__ void __launch_bounds__(MG * COL_WARPS * 32) attention_latent_tiled_ke
         }
         // ---- output: P [16 x 64] times this warp's columns of V
         {
-            const __nv_bfloat16* p_lane = p_s + (size_t)(mg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * P_STRIDE + (lane >> 4) * 8;
-            const __nv_bfloat16* v_lane = kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + col0 + (lane >> 4) * 8;
+            const uint32_t p_at = smem_u32(p_s + (size_t)(mg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * P_STRIDE + (lane >> 4) * 8);
+            const uint32_t v_at = smem_u32(kt + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * stride + col0 + (lane >> 4) * 8);
+            const uint32_t v_step = 16 * stride * 2;  // bytes from one group of 16 keys to the next
 #pragma unroll
             for (int kk = 0; kk < PAGE / 16; ++kk) {
                 uint32_t pa[4], vb[2][4];  // after unrolling every index below is a constant
-                ldmatrix_x4(pa, p_lane + kk * 16);
-                ldmatrix_x4_trans(vb[0], v_lane + (size_t)kk * 16 * stride);
+                ldmatrix_x4_at(pa, p_at + kk * 32);
+                ldmatrix_x4_trans_at(vb[0], v_at + kk * v_step);
 #pragma unroll
                 for (int n = 0; n < NT; n += 2)
                     if (n < nt_used) {
-                        if (n + 2 < nt_used) ldmatrix_x4_trans(vb[((n >> 1) + 1) & 1], v_lane + (size_t)kk * 16 * stride + (n + 2) * 8);
+                        if (n + 2 < nt_used) ldmatrix_x4_trans_at(vb[((n >> 1) + 1) & 1], v_at + kk * v_step + (n + 2) * 16);
                         mma_16816(o[n], pa, vb[(n >> 1) & 1][0], vb[(n >> 1) & 1][1]);
                         mma_16816(o[n + 1], pa, vb[(n >> 1) & 1][2], vb[(n >> 1) & 1][3]);
                     }
