@@ -218,3 +218,17 @@ def test_command_line_generates_the_greedy_tokens():
         if (top[0] - top[1]).item() > 1e-3:
             assert int(logits.argmax()) == token
         sequence.append(token)
+
+
+@pytest.mark.parametrize("tag,dtype", [("das_e", "bfloat16"), ("das_a", "float32")])
+def test_a_prompt_shape_seen_again_replays_from_a_graph(tag, dtype):
+    """A many-token step is captured when its shape comes a second time and replayed from then on: other prompts of the
+    same length, in slots that were used before, give the plain implementation's logits each time."""
+    engine = das_engine(tag, dtype, max_tokens=256, max_seqs=2)
+    poison(engine)
+    for r, tokens in enumerate(das_requests(tag, [83, 83, 83, 83], seed=17)):
+        logits = engine.step([_entry(r, tokens, [0, 41, 82])])
+        engine.end([r])
+        das_check(tag, dtype, tokens, [0, 41, 82], logits, f"{tag} {dtype} prompt {r} of one shape")
+    assert engine.graphs is not None and any(key[3] == 83 for key in engine.graphs.graphs)
+    engine.check()
