@@ -738,7 +738,7 @@ def _kernel_table(d: dict, t: dict, peak: dict) -> dict:
         ms = _event_ms(lambda: F.branch_merge(x, y, ones, 1e-6, ones, next_weight=ones, next_eps=1e-6, next_dtype=torch.bfloat16), flush=flush, inner=inner)
         record(f"dasusun branch merge with next norm, {label}", ms, tokens * w * (4 + 2 + 4 + 2))
         state = torch.zeros(n_seqs, 3, w, device=dev)
-        conv_w = torch.randn(w, 4, device=dev)
+        conv_w = torch.randn(4, w, device=dev)
         ms = _event_ms(lambda: F.causal_conv(x, conv_w, state, tok_pos, tok_seq, cu_q, slots, torch.bfloat16), flush=flush, inner=inner)
         record(f"dasusun causal convolution (4 taps), {label}", ms, tokens * w * (4 + 2))
         proj = torch.randn(tokens, d["q_rank"] + r + rot, device=dev).bfloat16()

@@ -1080,7 +1080,8 @@ def branch_merge(x: torch.Tensor, y: torch.Tensor, norm_weight: torch.Tensor, ep
 
 def causal_conv(a: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
                 cu_q: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype, update_single_token_state: bool = False) -> torch.Tensor:
-    """``a + conv(a)`` over time on each channel: ``a [n_tokens, width]`` 32-bit, ``weight [width, taps]`` 32-bit,
+    """``a + conv(a)`` over time on each channel: ``a [n_tokens, width]`` 32-bit, ``weight [taps, width]`` 32-bit (tap by tap, so
+    that neighbouring channels' weights lie side by side),
     ``state [n_slots, taps - 1, width]`` the sequences' inputs of before (read only; ``conv_state`` brings it up to date
     afterwards).  ``update_single_token_state``: every sequence of the step brings exactly one token, and the kernel moves
     the states on itself."""
@@ -1088,8 +1089,8 @@ def causal_conv(a: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | Non
     _check(a, "a", torch.float32, 2)
     _check(weight, "weight", torch.float32, 2)
     n, width = a.shape
-    taps = weight.shape[1]
-    if weight.shape[0] != width:
+    taps = weight.shape[0]
+    if weight.shape[1] != width:
         raise KernelError(f"convolution weights {tuple(weight.shape)} for rows of {width}")
     if taps > 1:
         _check(state, "state", torch.float32, 3)

@@ -150,7 +150,7 @@ class SandwichBlock(Block):
         if self.feed_forward is not None:
             self.scale_2 = tensors[n["scale_2"]].float().contiguous()
         if self.conv_taps:
-            self.conv = tensors[n["conv"]].float().contiguous()
+            self.conv = tensors[n["conv"]].float().t().contiguous()  # [taps, width]: the kernels read tap by tap
 
     def weight_bytes(self):
         own = sum(t.numel() * t.element_size() for t in (self.scale_1, self.scale_2, self.conv, self.mix) if t is not None)

@@ -21,7 +21,7 @@ def _f():
     return F
 
 
-@pytest.mark.parametrize("width,rows", [(96, 5), (1000, 3), (4096, 2)])
+@pytest.mark.parametrize("width,rows", [(96, 5), (97, 4), (1000, 3), (4096, 2)])  # 97: the one-element kernel
 @pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
 def test_branch_merge(width, rows, y_dtype):
     F = _f()
@@ -53,10 +53,11 @@ def test_branch_merge(width, rows, y_dtype):
 
 
 @pytest.mark.parametrize("taps", [1, 2, 3, 5])
-def test_causal_convolution_with_state_under_every_cut(taps):
+@pytest.mark.parametrize("width", [40, 41])  # four channels a thread, and the one-channel kernel
+def test_causal_convolution_with_state_under_every_cut(taps, width):
     """Three sequences of unequal lengths fed in portions (also shorter than the taps) give what each gives whole."""
     F = _f()
-    width, n_slots = 40, 6
+    n_slots = 6
     gen = torch.Generator().manual_seed(taps)
     w = torch.randn(width, taps, generator=gen)
     lengths = [11, 1, 7]
@@ -77,7 +78,7 @@ def test_causal_convolution_with_state_under_every_cut(taps):
         tok_pos = torch.cat([torch.arange(done[i], done[i] + portion[i]) for i in live]).int().to(DEV)
         slot_t = torch.tensor([slots[i] for i in live], dtype=torch.int32, device=DEV)
         single = all(n == 1 for n in q)  # one token each: the convolution's kernel moves the states on itself
-        out = F.causal_conv(rows, w.to(DEV), state if taps > 1 else None, tok_pos, tok_seq, cu, slot_t, torch.float32,
+        out = F.causal_conv(rows, w.t().contiguous().to(DEV), state if taps > 1 else None, tok_pos, tok_seq, cu, slot_t, torch.float32,
                             update_single_token_state=single and taps > 1)
         if taps > 1 and not single:
             F.conv_state(rows, state, cu, slot_t, len(live))
