@@ -223,3 +223,72 @@ GK_EXPORT int gk_attention_latent_exact(const void* q_carried, long long qc_tok,
     GK_CHECK_LAUNCH("attention_latent_exact");
     return GK_OK;
 }
+
+// ---- a batch of small products, one per head, for steps of a few tokens:  out[b][m][n] = sum_k x[b][m][k] * w[b][n][k]
+// (bfloat16 in, 32-bit sums, rounded once).  x and out are views with batch and row strides (heads lie side by
+// side in a token's row); w is contiguous [B, N, K].  One thread per output: with a handful of tokens the products are a
+// few hundred kilobytes of weights, read through the L2 once per token, and next to no arithmetic.  (32-bit sums, four
+// partial sums an output in a fixed order.)
+namespace {
+
+// Four lanes an output: lane q of the quad takes the 8-element pieces q, q + 4, q + 8, ... of the row (all its loads
+// independent of one another), and the four partial sums meet by two shuffles in a fixed order.
+template <bool VEC>
+__global__ void heads_product_kernel(const __nv_bfloat16* __restrict__ x, long long x_batch, long long x_row,
+                                     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long o_batch,
+                                     long long o_row, int batch, int m, int n, int k) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 2;
+    const int q = threadIdx.x & 3;
+    const bool on = idx < (long long)batch * m * n;  // whole quads are on or off; off lanes still take part in the shuffles
+    const long long at = on ? idx : 0;
+    const int col = (int)(at % n);
+    const int tok = (int)((at / n) % m);
+    const int b = (int)(at / ((long long)n * m));
+    const __nv_bfloat16* xr = x + (size_t)b * x_batch + (size_t)tok * x_row;
+    const __nv_bfloat16* wr = w + ((size_t)b * n + col) * k;
+    float acc = 0.f;
+    if (VEC) {
+#pragma unroll 4
+        for (int i = q * 8; i < k; i += 32) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xr + i), wv = *reinterpret_cast<const uint4*>(wr + i);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float2 xf = __bfloat1622float2(xp[c]), wf = __bfloat1622float2(wp[c]);
+                acc = fmaf(xf.x, wf.x, acc);
+                acc = fmaf(xf.y, wf.y, acc);
+            }
+        }
+    } else {
+#pragma unroll 4
+        for (int i = q; i < k; i += 4) acc = fmaf(__bfloat162float(xr[i]), __bfloat162float(wr[i]), acc);
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (on && q == 0) out[(size_t)b * o_batch + (size_t)tok * o_row + col] = __float2bfloat16_rn(acc);
+}
+
+}  // namespace
+
+GK_EXPORT int gk_heads_product_bf16(const void* x, long long x_batch, long long x_row, const void* w, void* out, long long o_batch,
+                                    long long o_row, int batch, int m, int n, int k, void* stream) {
+    GK_REQUIRE(batch > 0 && m >= 0 && n > 0 && k > 0, "heads_product: bad sizes batch=%d m=%d n=%d k=%d", batch, m, n, k);
+    const long long total = (long long)batch * m * n;
+    if (total == 0) return GK_OK;
+    const int threads = 128;
+    const long long blocks = (total * 4 + threads - 1) / threads;
+    GK_REQUIRE(blocks < 2147483647LL, "heads_product: too many outputs");
+    const bool vec = k % 8 == 0 && x_batch % 8 == 0 && x_row % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (vec)
+        gk_launch(heads_product_kernel<true>, dim3((unsigned)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)x, x_batch, x_row,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_batch, o_row, batch, m, n, k);
+    else
+        gk_launch(heads_product_kernel<false>, dim3((unsigned)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)x, x_batch, x_row,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_batch, o_row, batch, m, n, k);
+    GK_CHECK_LAUNCH("heads_product");
+    return GK_OK;
+}

@@ -1175,7 +1175,8 @@ def attention_latent_exact(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_a
 def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[b] = x[b] @ weight[b].T`` for a batch of products (one per head): ``x [B, M, K]`` and ``out [B, M, N]`` may be
     views with any batch and row strides (innermost contiguous), ``weight [B, N, K]`` is contiguous.  float32 weights go
-    through the FP32-pipe kernel, bfloat16 ones through the library's batched product with 32-bit accumulation."""
+    through the FP32-pipe kernel; bfloat16 ones through this library's small-product kernel for a few tokens (as the
+    few-token product serves the projections) and through the library's batched product for many, both with 32-bit sums."""
     require_device(x.device)
     b, m, k = x.shape
     n = weight.shape[1]
@@ -1188,6 +1189,10 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
         return out
     if weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("a bfloat16 batched product needs bfloat16 operands and output")
+    if m <= GEMV_MAX_TOKENS:
+        call("gk_heads_product_bf16", ptr(x), x.stride(0), x.stride(1), ptr(weight), ptr(out), out.stride(0), out.stride(1), b, m, n, k,
+             stream_ptr())
+        return out
     torch.bmm(x, weight.transpose(1, 2), out=out)
     return out
 

@@ -41,6 +41,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_causal_conv": [P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "gk_conv_state": [P, P, P, P, I, I, I, P],
     "gk_gelu_tanh": [P, P, I, L, P],
+    "gk_heads_product_bf16": [P, L, L, P, P, L, L, I, I, I, I, P],
     "gk_latent_prepare": [P, I, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
     "gk_attention_latent_tiled": [P, L, L, P, I, I, P, P, P, P, L, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_latent_exact": [P, L, L, P, I, I, P, P, P, P, L, L, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],

@@ -254,3 +254,20 @@ def test_latent_attention_one_key_decides(dtype, window, heads, rank, rot):
     assert torch.allclose(together, want, **tol)
     for n in range(0, len(queries), 7):  # a sample of them as single-token steps
         assert torch.allclose(run([n])[0], want[n], **tol), f"position {queries[n][0]} target {queries[n][1]} alone"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens", [1, 7, 16, 40])
+@pytest.mark.parametrize("heads,n,k,pad", [(3, 40, 24, 8), (5, 17, 13, 3), (16, 64, 128, 32)])
+def test_per_head_products_on_strided_views(dtype, tokens, heads, n, k, pad):
+    """One product per head on operands that lie side by side in a token's row, written into a strided view: few tokens take
+    the small-product kernel, many the batched product, float32 the FP32-pipe kernel; all against the plain sum."""
+    F = _f()
+    gen = torch.Generator().manual_seed(tokens * 100 + heads)
+    rows = torch.randn(tokens, heads, k + pad, generator=gen).to(dtype)       # a head's operand is the first k of its part
+    w = (torch.randn(heads, n, k, generator=gen) * 0.3).to(dtype)
+    out = torch.full((tokens, heads * n), float("nan"), dtype=dtype, device=DEV)
+    F.linear_batched(rows.to(DEV)[:, :, :k].transpose(0, 1), w.to(DEV), out.view(tokens, heads, n).transpose(0, 1))
+    want = torch.einsum("thk,hnk->thn", rows[:, :, :k].double(), w.double()).reshape(tokens, heads * n)
+    tol = dict(atol=1e-4, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.05, rtol=0.01)
+    assert torch.allclose(out.double().cpu(), want, **tol)
