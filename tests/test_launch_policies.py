@@ -119,3 +119,22 @@ def test_the_even_deal_for_a_few_long_sequences():
     assert not decode_flat_wins(4, 8, 7168, 64, 148, places, 296) and not decode_flat_wins(4, 8, 5120, 64, 148, places, 296)
     for length in (10240, 20480, 36864):
         assert not decode_flat_wins(1, 8, length, 64, 148, places, 296) and not decode_flat_wins(2, 8, length, 64, 148, places, 296)
+
+
+def test_latent_attention_splits():
+    """Single-token steps of latent attention: enough blocks for the device, never more than a page each, at most 16."""
+    from gtar_kimik3_public_b200.ops.functional import LATENT_TILED_MAX_SPLITS, latent_splits
+
+    sms = 148
+    assert latent_splits(8, 16, 2048, 1024, sms) == 16          # 8 tiles: the device wants 37 blocks a tile, 17 pages, capped
+    assert latent_splits(8, 16, 2048, 0, sms) == 16             # no window: the whole context
+    assert latent_splits(1, 4, 100, 40, sms) == 1               # a window inside one page
+    assert latent_splits(1, 4, 100, 0, sms) == 2                # 100 keys: two pages
+    assert latent_splits(64, 32, 4096, 0, sms) == 2             # 128 tiles: two blocks a tile fill the device
+    assert latent_splits(256, 16, 4096, 0, sms) == 1
+    for n_seqs in (1, 3, 17, 200):
+        for heads in (1, 16, 40):
+            for kv_len, window in ((1, 0), (64, 0), (65, 64), (5000, 0), (5000, 130)):
+                splits = latent_splits(n_seqs, heads, kv_len, window, sms)
+                span = min(kv_len, window) if window else kv_len
+                assert 1 <= splits <= min(LATENT_TILED_MAX_SPLITS, span // 64 + 1)
