@@ -13,6 +13,9 @@ values) over its time, against the measured copy bandwidth.
 Weights are random (written as a model folder by the library's random-weights mode and loaded
 from there), token ids are seeded uniform-random: there is no network for checkpoints or data.
 The library runs on one GPU; with --gpus N > 1 a line says so and the exit code is 2.
+
+``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
+at equal layer sizes (prefill and decode throughput of both, and the new design's kernels one by one against their rooflines).
 """
 
 from __future__ import annotations

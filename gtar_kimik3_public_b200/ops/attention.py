@@ -4,6 +4,10 @@
   work gives bit-equal results);
 * bfloat16, every sequence bringing one token: the split-KV decode kernel;
 * bfloat16 otherwise (prompts, or continuations of several tokens): the flash prefill kernel.
+
+Layers that keep one latent row per position for all heads (``latent_attention`` below): bfloat16 rows whose sizes the
+tensor-core kernel takes go there, prompts and single tokens alike (single-token steps cut into splits); everything else, and
+every float32 run, goes to the exact latent kernel.
 """
 
 from __future__ import annotations
