@@ -5,6 +5,8 @@
 // For a token at position pos of its sequence, query head hq, kv head hk = hq / (n_q / n_kv):
 //   s_j = (q . k_j) * scale      for the visible keys j <= pos (and j > pos - window, if a window is set)
 //   o   = sum_j softmax(s)_j v_j
+// With `sink` the softmax has one more term in its denominator, a key of score 0 that has no value:
+//   p_j = exp(s_j) / (1 + sum_i exp(s_i)).
 // which is the rule  key j visible to query i iff j <= past + i  of the reference
 // (src/layers/attention.py:116-119) with consecutive query heads sharing a kv head
 // (src/ops/flash_attention_2.py:33-34), scale = head_dim^-0.5 (flash_attention_2.py:216).
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_exact_kernel(
     const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages, T* __restrict__ out,
     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
     const int* __restrict__ block_table, int n_tokens, int n_q, int n_kv, int head_dim, int max_pages, int page_size,
-    float scale, int window) {
+    float scale, int window, int sink) {
     extern __shared__ float q_smem[];  // WARPS * head_dim
     pdl_launch_dependents();
     pdl_wait();
@@ -111,6 +113,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_exact_kernel(
         }
         m = m_new;
     }
+    if (sink) l += expf(-m);  // the term of score 0, against the same reference exponent as the others
     T* orow = out + ((size_t)t * n_q + hq) * head_dim;
 #pragma unroll
     for (int c = 0; c < MAX_ACC; ++c) {
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_exact_kernel(
 GK_EXPORT int gk_attention_exact(const void* q, const void* k_pages, const void* v_pages, void* out, int dtype,
                                  const int* tok_pos, const int* tok_seq, const int* slots, const int* block_table,
                                  int n_tokens, int n_q, int n_kv, int head_dim, int max_pages, int page_size,
-                                 float scale, int window, void* stream) {
+                                 float scale, int window, int sink, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype), "attention_exact: bad dtype %d", dtype);
     GK_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_exact: bad head counts %d/%d", n_q,
                n_kv);
@@ -142,7 +145,7 @@ GK_EXPORT int gk_attention_exact(const void* q, const void* k_pages, const void*
     GK_DISPATCH_DTYPE(dtype, T, {
         gk_launch(attention_exact_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, s,
             (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, tok_pos, tok_seq, slots, block_table, n_tokens,
-            n_q, n_kv, head_dim, max_pages, page_size, scale, window);
+            n_q, n_kv, head_dim, max_pages, page_size, scale, window, sink);
     })
     GK_CHECK_LAUNCH("attention_exact");
     return GK_OK;

@@ -11,24 +11,24 @@
 // ---------------------------------------------------------------- embedding gather
 template <typename TT>
 __global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                  int hidden) {
+                                  int hidden, float scale) {
     pdl_launch_dependents();  // the next kernel may take its place on the SMs and fetch what does not depend on this one
     pdl_wait();
     const int t = blockIdx.x;
     const TT* row = table + (size_t)ids[t] * hidden;
     float* dst = out + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]) * scale;
 }
 
 GK_EXPORT int gk_embed_rows(const void* table, int table_dtype, const int* ids, float* out, int n_tokens, int hidden,
-                            void* stream) {
+                            float scale, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(table_dtype), "embed_rows: bad table dtype %d", table_dtype);
     GK_REQUIRE(n_tokens >= 0 && hidden > 0, "embed_rows: bad sizes n_tokens=%d hidden=%d", n_tokens, hidden);
     if (n_tokens == 0) return GK_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     GK_DISPATCH_DTYPE(table_dtype, TT, {
         gk_launch(embed_rows_kernel<TT>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const TT*)table, ids, out,
-                  hidden);
+                  hidden, scale);
     })
     GK_CHECK_LAUNCH("embed_rows");
     return GK_OK;

@@ -1,0 +1,247 @@
+// A feed-forward of many small gated experts of which every token uses a few.
+//
+//   route        z = W_r h in 32-bit, s = sigmoid(z), choice = s + correction.  The experts form equal groups of
+//                neighbours; a group's score is the sum of its two largest choice scores and only the experts of the best
+//                `keep` groups may be chosen.  The `top` largest choice scores among them are chosen (ties: the lower
+//                index); a chosen expert's weight is its s (without the correction) times a constant.  One warp per token.
+//   experts_up   act[pair] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair (token, chosen expert)
+//   experts_down out_t = add_t + sum over the token's pairs, in the order they were chosen, of weight * W_down[e] act[pair]
+//                (32-bit result: it is what goes into the residual stream)
+//
+// The two expert kernels take a pair at a time, one warp per output row: the path of single-token steps, of 32-bit
+// runs and of sizes the tensor-core path does not take.  A token's result depends on the token alone.
+//
+//   sort         pairs ordered by expert for the tensor-core path: counts, starts (padded to a multiple of the tile rows),
+//                and the list of pairs of each expert
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(
+    const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction, int* __restrict__ ids,
+    float* __restrict__ weights, int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale) {
+    extern __shared__ float route_smem[];  // per warp: s [E] | choice [E] | group score [n_groups]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= n_tokens) return;
+    float* s = route_smem + (size_t)warp * (2 * n_experts + n_groups);
+    float* choice = s + n_experts;
+    float* group_score = choice + n_experts;
+    const T* x = h + (size_t)t * width;
+    for (int e = 0; e < n_experts; ++e) {
+        const float* w = w_router + (size_t)e * width;
+        float acc = 0.f;
+        for (int i = lane; i < width; i += 32) acc = fmaf(to_float(x[i]), w[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float sg = 1.f / (1.f + expf(-acc));
+            s[e] = sg;
+            choice[e] = sg + correction[e];
+        }
+    }
+    __syncwarp();
+    const int per = n_experts / n_groups;
+    if (n_groups > 1 && keep < n_groups) {
+        for (int gidx = lane; gidx < n_groups; gidx += 32) {
+            float first = -INFINITY, second = -INFINITY;
+            for (int e = gidx * per; e < (gidx + 1) * per; ++e) {
+                const float c = choice[e];
+                if (c > first) { second = first; first = c; }
+                else if (c > second) second = c;
+            }
+            group_score[gidx] = per > 1 ? first + second : first;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            // the groups that are not among the best `keep` lose their experts
+            for (int gidx = 0; gidx < n_groups; ++gidx) {
+                int better = 0;
+                for (int o = 0; o < n_groups; ++o)
+                    better += (group_score[o] > group_score[gidx]) || (group_score[o] == group_score[gidx] && o < gidx);
+                if (better >= keep)
+                    for (int e = gidx * per; e < (gidx + 1) * per; ++e) choice[e] = -INFINITY;
+            }
+        }
+        __syncwarp();
+    }
+    for (int pick = 0; pick < top; ++pick) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float c = choice[e];
+            if (c > best) { best = c; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = 0;  // nothing left to choose from: cannot happen when top <= allowed experts
+        if (lane == 0) {
+            ids[(size_t)t * top + pick] = arg;
+            weights[(size_t)t * top + pick] = s[arg] * scale;
+            choice[arg] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+template <typename TW>
+__device__ __forceinline__ float dot_smem(const float* __restrict__ x, const TW* __restrict__ w, int n, int lane);
+
+template <>
+__device__ __forceinline__ float dot_smem<float>(const float* __restrict__ x, const float* __restrict__ w, int n, int lane) {
+    float acc = 0.f;
+    if ((n & 3) == 0) {
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 a = *reinterpret_cast<const float4*>(w + i);
+            acc = fmaf(x[i], a.x, acc); acc = fmaf(x[i + 1], a.y, acc); acc = fmaf(x[i + 2], a.z, acc); acc = fmaf(x[i + 3], a.w, acc);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc = fmaf(x[i], w[i], acc);
+    }
+    return warp_sum(acc);
+}
+
+template <>
+__device__ __forceinline__ float dot_smem<__nv_bfloat16>(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int lane) {
+    float acc = 0.f;
+    if ((n & 7) == 0) {
+        for (int i = lane * 8; i < n; i += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float2 f = __bfloat1622float2(p[c]);
+                acc = fmaf(x[i + 2 * c], f.x, acc);
+                acc = fmaf(x[i + 2 * c + 1], f.y, acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc = fmaf(x[i], __bfloat162float(w[i]), acc);
+    }
+    return warp_sum(acc);
+}
+
+constexpr int UP_WARPS = 8;
+
+// grid (pairs, chunks of ff): w_gate_up [E, 2, ff, width] (gate rows then up rows of an expert)
+template <typename T, typename TW>
+__global__ void __launch_bounds__(UP_WARPS * 32) experts_up_kernel(
+    const T* __restrict__ h, const TW* __restrict__ w_gate_up, const int* __restrict__ ids, T* __restrict__ act, int width,
+    int ff, int top, int rows_per_block) {
+    extern __shared__ __align__(16) float xs[];  // width
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pair = blockIdx.x, t = pair / top;
+    const int e = ids[pair];
+    for (int i = threadIdx.x; i < width; i += UP_WARPS * 32) xs[i] = to_float(h[(size_t)t * width + i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TW* wg = w_gate_up + (size_t)e * 2 * ff * width;
+    const TW* wu = wg + (size_t)ff * width;
+    const int f0 = blockIdx.y * rows_per_block;
+    for (int f = f0 + warp; f < min(ff, f0 + rows_per_block); f += UP_WARPS) {
+        const float gate = dot_smem<TW>(xs, wg + (size_t)f * width, width, lane);
+        const float up = dot_smem<TW>(xs, wu + (size_t)f * width, width, lane);
+        if (lane == 0) act[(size_t)pair * ff + f] = from_float<T>(gate / (1.f + expf(-gate)) * up);
+    }
+}
+
+// grid (tokens, chunks of width): w_down [E, width, ff]
+template <typename T, typename TW>
+__global__ void __launch_bounds__(UP_WARPS * 32) experts_down_kernel(
+    const T* __restrict__ act, const TW* __restrict__ w_down, const int* __restrict__ ids, const float* __restrict__ weights,
+    const T* __restrict__ add, float* __restrict__ out, int width, int ff, int top, int rows_per_block) {
+    extern __shared__ __align__(16) float as[];  // top * ff
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < top * ff; i += UP_WARPS * 32) as[i] = to_float(act[(size_t)t * top * ff + i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = blockIdx.y * rows_per_block;
+    for (int c = c0 + warp; c < min(width, c0 + rows_per_block); c += UP_WARPS) {
+        float acc = add != nullptr ? to_float(add[(size_t)t * width + c]) : 0.f;
+        for (int kk = 0; kk < top; ++kk) {
+            const int e = ids[(size_t)t * top + kk];
+            const float d = dot_smem<TW>(as + (size_t)kk * ff, w_down + ((size_t)e * width + c) * ff, ff, lane);
+            acc = fmaf(weights[(size_t)t * top + kk], d, acc);
+        }
+        if (lane == 0) out[(size_t)t * width + c] = acc;
+    }
+}
+
+}  // namespace
+
+GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, const float* correction, int* ids, float* weights,
+                              int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype), "route_groups: bad dtype %d", dtype);
+    GK_REQUIRE(n_experts > 0 && top > 0 && top <= n_experts, "route_groups: %d of %d experts", top, n_experts);
+    GK_REQUIRE(n_groups >= 1 && n_experts % n_groups == 0 && keep >= 1 && keep <= n_groups, "route_groups: %d groups, %d kept, %d experts",
+               n_groups, keep, n_experts);
+    GK_REQUIRE(top <= keep * (n_experts / n_groups), "route_groups: %d experts cannot come from %d groups of %d", top, keep,
+               n_experts / n_groups);
+    if (n_tokens == 0) return GK_OK;
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * n_experts + n_groups) * sizeof(float);
+    GK_REQUIRE(smem <= 48 * 1024, "route_groups: too many experts (%d)", n_experts);
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        gk_launch(route_kernel<T>, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, s, (const T*)h,
+                  w_router, correction, ids, weights, n_tokens, width, n_experts, top, n_groups, keep, scale);
+    })
+    GK_CHECK_LAUNCH("route_groups");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_experts_up(const void* h, int dtype, const void* w_gate_up, int w_dtype, const int* ids, void* act, int n_tokens,
+                            int width, int ff, int top, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(w_dtype), "experts_up: bad dtype");
+    GK_REQUIRE(width > 0 && ff > 0 && top > 0, "experts_up: bad sizes");
+    if (n_tokens == 0) return GK_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    GK_REQUIRE(smem <= 48 * 1024, "experts_up: rows of %d are longer than the kernel stages", width);
+    // few pairs: cut the expert's rows over more blocks, so that a single token still finds every SM a share
+    const long long pairs = (long long)n_tokens * top;
+    int chunks = 1;
+    while (pairs * chunks < 592 && ff / (chunks * 2) >= UP_WARPS) chunks *= 2;
+    const int rows = (ff + chunks - 1) / chunks;
+    GK_REQUIRE(pairs < 2147483647LL, "experts_up: too many pairs");
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        GK_DISPATCH_DTYPE(w_dtype, TW, {
+            gk_launch(experts_up_kernel<T, TW>, dim3((unsigned)pairs, (ff + rows - 1) / rows), dim3(UP_WARPS * 32), smem, s, (const T*)h,
+                      (const TW*)w_gate_up, ids, (T*)act, width, ff, top, rows);
+        })
+    })
+    GK_CHECK_LAUNCH("experts_up");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_experts_down(const void* act, int dtype, const void* w_down, int w_dtype, const int* ids, const float* weights,
+                              const void* add, float* out, int n_tokens, int width, int ff, int top, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(w_dtype), "experts_down: bad dtype");
+    GK_REQUIRE(width > 0 && ff > 0 && top > 0, "experts_down: bad sizes");
+    if (n_tokens == 0) return GK_OK;
+    const size_t smem = (size_t)top * ff * sizeof(float);
+    GK_REQUIRE(smem <= 48 * 1024, "experts_down: %d experts of %d are more than the kernel stages", top, ff);
+    int chunks = 1;
+    while ((long long)n_tokens * chunks < 592 && width / (chunks * 2) >= UP_WARPS) chunks *= 2;
+    const int rows = (width + chunks - 1) / chunks;
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        GK_DISPATCH_DTYPE(w_dtype, TW, {
+            gk_launch(experts_down_kernel<T, TW>, dim3(n_tokens, (width + rows - 1) / rows), dim3(UP_WARPS * 32), smem, s, (const T*)act,
+                      (const TW*)w_down, ids, weights, (const T*)add, out, width, ff, top, rows);
+        })
+    })
+    GK_CHECK_LAUNCH("experts_down");
+    return GK_OK;
+}

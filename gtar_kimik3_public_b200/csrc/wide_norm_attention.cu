@@ -1,0 +1,136 @@
+// What an attention layer with one norm over the whole query projection and one over the whole key projection,
+// values that ARE the keys as projected, and a gate on its result needs around the attention kernel:
+//
+//   wide_norm_rope_write   per token: q <- w_q * q / sqrt(mean(q^2) + eps) over all query heads at once, the same for
+//                          k over all key heads; then, in each head, the first `rot` entries turn by the token's
+//                          position (entry i paired with i + rot/2; cos and sin from tables [positions, rot/2]) and the
+//                          rest pass; the finished key goes into the key pages and the key AS PROJECTED (before norm
+//                          and rotation) into the value pages.  One block per token, 32-bit arithmetic.
+//   sigmoid_gate           out = o * sigmoid(gate), the gate read from a column range of a wider row
+//   softcap                x <- cap * tanh(x / cap), in place (32-bit logits)
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WN_THREADS = 256;
+
+template <typename T, typename TC>
+__global__ void __launch_bounds__(WN_THREADS) wide_norm_rope_write_kernel(
+    const T* __restrict__ proj, long long ld, const float* __restrict__ w_q, const float* __restrict__ w_k,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
+    const int* __restrict__ tok_seq, const int* __restrict__ slots, const int* __restrict__ block_table,
+    T* __restrict__ q_out, TC* __restrict__ k_pages, TC* __restrict__ v_pages, int n_q, int n_kv, int d, int rot,
+    int max_pages, int page_size, float eps) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T* row = proj + (size_t)t * ld;
+    const int nq = n_q * d, nk = n_kv * d;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += WN_THREADS) { const float v = to_float(row[i]); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < nk; i += WN_THREADS) { const float v = to_float(row[nq + i]); sk = fmaf(v, v, sk); }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    const float rq = 1.f / sqrtf(sq / (float)nq + eps), rk = 1.f / sqrtf(sk / (float)nk + eps);
+    const int pos = tok_pos[t];
+    const int half = rot >> 1;
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    for (int i = threadIdx.x; i < nq + nk; i += WN_THREADS) {
+        const bool is_q = i < nq;
+        const int at = is_q ? i : i - nq;
+        const int j = at % d;
+        const float r = is_q ? rq : rk;
+        const float* w = is_q ? w_q : w_k;
+        const float mine = to_float(row[i]) * r * w[at];
+        float res = mine;
+        if (j < half) {
+            const float other = to_float(row[i + half]) * r * w[at + half];
+            res = mine * cs[j] - other * sn[j];
+        } else if (j < rot) {
+            const float other = to_float(row[i - half]) * r * w[at - half];
+            res = mine * cs[j - half] + other * sn[j - half];
+        }
+        if (is_q) {
+            q_out[(size_t)t * nq + at] = from_float<T>(res);
+        } else if (k_pages != nullptr) {
+            const int hk = at / d;
+            const int page = block_table[(size_t)slots[tok_seq[t]] * max_pages + pos / page_size];
+            const size_t dst = (((size_t)page * n_kv + hk) * page_size + pos % page_size) * d + j;
+            k_pages[dst] = from_float<TC>(res);
+            v_pages[dst] = from_float<TC>(to_float(row[i]));
+        }
+    }
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ o, const T* __restrict__ gate, long long ld_gate, T* __restrict__ out,
+                                    long long n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    const float g = to_float(gate[t * ld_gate + c]);
+    out[i] = from_float<T>(to_float(o[i]) / (1.f + expf(-g)));
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+}  // namespace
+
+GK_EXPORT int gk_wide_norm_rope_write(const void* proj, int dtype, long long ld, const float* w_q, const float* w_k,
+                                      const float* cos_t, const float* sin_t, int table_positions, const int* tok_pos,
+                                      const int* tok_seq, const int* slots, const int* block_table, void* q_out, void* k_pages,
+                                      void* v_pages, int cache_dtype, int n_tokens, int n_q, int n_kv, int d, int rot,
+                                      int max_pages, int page_size, float eps, int max_position, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(cache_dtype), "wide_norm_rope_write: bad dtype");
+    GK_REQUIRE(n_q > 0 && n_kv > 0 && d > 0, "wide_norm_rope_write: bad sizes");
+    GK_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, "wide_norm_rope_write: %d rotated entries in heads of %d", rot, d);
+    GK_REQUIRE(rot == 0 || (cos_t != nullptr && sin_t != nullptr && max_position < table_positions),
+               "wide_norm_rope_write: position %d is beyond the rotation tables (%d)", max_position, table_positions);
+    if (n_tokens == 0) return GK_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        GK_DISPATCH_DTYPE(cache_dtype, TC, {
+            gk_launch(wide_norm_rope_write_kernel<T, TC>, dim3(n_tokens), dim3(WN_THREADS), 0, s, (const T*)proj, ld, w_q, w_k, cos_t,
+                      sin_t, tok_pos, tok_seq, slots, block_table, (T*)q_out, (TC*)k_pages, (TC*)v_pages, n_q, n_kv, d, rot, max_pages,
+                      page_size, eps);
+        })
+    })
+    GK_CHECK_LAUNCH("wide_norm_rope_write");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_sigmoid_gate(const void* o, const void* gate, long long ld_gate, void* out, int dtype, long long n_tokens, int width,
+                              void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && width > 0, "sigmoid_gate: bad arguments");
+    if (n_tokens == 0) return GK_OK;
+    const long long n = n_tokens * width;
+    const long long blocks = (n + 255) / 256;
+    GK_REQUIRE(blocks < 2147483647LL, "sigmoid_gate: too many elements");
+    GK_DISPATCH_DTYPE(dtype, T, {
+        gk_launch(sigmoid_gate_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)o, (const T*)gate, ld_gate,
+                  (T*)out, n, width);
+    })
+    GK_CHECK_LAUNCH("sigmoid_gate");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_softcap(float* x, long long n, float cap, void* stream) {
+    GK_REQUIRE(cap > 0.f, "softcap: the cap must be positive");
+    if (n == 0) return GK_OK;
+    const long long blocks = (n + 255) / 256;
+    GK_REQUIRE(blocks < 2147483647LL, "softcap: too many elements");
+    gk_launch(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, n, cap);
+    GK_CHECK_LAUNCH("softcap");
+    return GK_OK;
+}

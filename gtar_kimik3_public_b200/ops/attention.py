@@ -51,11 +51,14 @@ def decode_flat_preferred(ctx, n_kv: int, kv: F.PagedKV) -> bool:
                               F.decode_flat_places(kv.k.shape[3], sms))
 
 
-def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: int = 0) -> torch.Tensor:
+def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: int = 0, sink: bool = False) -> torch.Tensor:
     """Causal grouped-query attention of the step's queries ``[n_tokens, n_q, d]`` over each
-    sequence's cached keys and values (the new tokens' own are already written)."""
+    sequence's cached keys and values (the new tokens' own are already written).  ``sink``: one more term in the
+    softmax's denominator (a key of score 0 without a value)."""
     n_q, d = q.shape[1], q.shape[2]
     n_kv = kv.k.shape[1]
+    if sink:
+        return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window, sink=True)
     fast = q.dtype == torch.bfloat16 and d in FAST_HEAD_DIMS and kv.page_size == 64 and n_q // n_kv <= 16
     if fast and ctx.all_single:
         if decode_flat_preferred(ctx, n_kv, kv):

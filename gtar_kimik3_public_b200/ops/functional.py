@@ -75,8 +75,8 @@ class DecodeWork:
         return self.part, self.tickets
 
 
-def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[t] = table[ids[t]]`` widened to float32 (the residual stream's type)."""
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """``out[t] = table[ids[t]] * scale`` widened to float32 (the residual stream's type) before the product."""
     require_device(table.device)
     _check(table, "table", dims=2)
     _check(ids, "ids", torch.int32, 1)
@@ -84,7 +84,7 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None 
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _check(out, "out", torch.float32, 2)
-    call("gk_embed_rows", ptr(table), dtype_code(table.dtype), ptr(ids), ptr(out), n, hidden, stream_ptr())
+    call("gk_embed_rows", ptr(table), dtype_code(table.dtype), ptr(ids), ptr(out), n, hidden, float(scale), stream_ptr())
     return out
 
 
@@ -305,8 +305,10 @@ def attention_exact(
     scale: float,
     window: int = 0,
     out: torch.Tensor | None = None,
+    sink: bool = False,
 ) -> torch.Tensor:
-    """Causal grouped-query attention of ``q [n_tokens, n_q, d]`` over the pages (exact kernel)."""
+    """Causal grouped-query attention of ``q [n_tokens, n_q, d]`` over the pages (exact kernel).  ``sink``: the
+    softmax's denominator has one more term, a key of score 0 without a value."""
     require_device(q.device)
     _check(q, "q", dims=3)
     n, n_q, d = q.shape
@@ -322,7 +324,7 @@ def attention_exact(
     call(
         "gk_attention_exact", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), dtype_code(q.dtype), ptr(tok_pos), ptr(tok_seq),
         ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),
-        stream_ptr(),
+        int(sink), stream_ptr(),
     )
     return out
 
@@ -1242,3 +1244,182 @@ def attention_latent_tiled(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_a
          ptr(cu_q), ptr(slots), ptr(cache.block_table), n, int(n_seqs), int(max_q_len), heads, rank, rot, rot_dims,
          cache.max_pages, cache.page_size, float(scale), int(window), int(splits), stream_ptr())
     return out
+
+
+# ------------------------------------------------------------------ the delta rule as a recurrent mixer
+def delta_prepare(proj: torch.Tensor, low: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor | None, a_log: torch.Tensor,
+                  dt_bias: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor, slots: torch.Tensor,
+                  n_heads: int, n_kv: int, d: int, dv: int, taps: int):
+    """Everything between the input projections and the recurrence, in 32-bit.  ``proj [T, >= 2 n_kv d + n_heads dv + n_heads]``
+    holds q | k | v | b of every token, ``low [T, >= n_heads d + n_heads dv]`` the decay's and the gate's second
+    projections; ``conv_w [channels, taps]``; ``conv_state [slots, taps - 1, channels]`` the inputs before the step.
+    Returns q, k ``[T, n_kv, d]`` (unit length; q also times ``d ** -0.5``), v ``[T, n_heads, dv]``, the decays
+    ``[T, n_heads, d]`` and beta ``[T, n_heads]``."""
+    require_device(proj.device)
+    _check(proj, "proj", dims=2)
+    _check(low, "low", dims=2)
+    T = proj.shape[0]
+    channels = 2 * n_kv * d + n_heads * dv
+    if proj.shape[1] < channels + n_heads or low.shape[1] < n_heads * (d + dv) or low.shape[0] != T:
+        raise KernelError(f"projections {tuple(proj.shape)} / {tuple(low.shape)} are too narrow for these sizes")
+    _check(conv_w, "conv_w", torch.float32, 2)
+    if tuple(conv_w.shape) != (channels, taps):
+        raise KernelError(f"conv_w is {tuple(conv_w.shape)}, expected {(channels, taps)}")
+    if taps > 1:
+        _check(conv_state, "conv_state", torch.float32, 3)
+        if tuple(conv_state.shape[1:]) != (taps - 1, channels):
+            raise KernelError(f"conv_state is {tuple(conv_state.shape)}, expected [slots, {taps - 1}, {channels}]")
+    _check(a_log, "a_log", torch.float32, 1)
+    _check(dt_bias, "dt_bias", torch.float32, 1)
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("cu_q", cu_q), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    dev = proj.device
+    q = torch.empty((T, n_kv, d), dtype=torch.float32, device=dev)
+    k = torch.empty((T, n_kv, d), dtype=torch.float32, device=dev)
+    v = torch.empty((T, n_heads, dv), dtype=torch.float32, device=dev)
+    g = torch.empty((T, n_heads, d), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, n_heads), dtype=torch.float32, device=dev)
+    call("gk_delta_prepare", ptr(proj), dtype_code(proj.dtype), proj.shape[1], ptr(low), dtype_code(low.dtype), low.shape[1],
+         ptr(conv_w), ptr(conv_state) if taps > 1 else None, ptr(a_log), ptr(dt_bias), ptr(tok_pos), ptr(tok_seq), ptr(cu_q),
+         ptr(slots), ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), T, n_heads, n_kv, d, dv, taps, stream_ptr())
+    return q, k, v, g, beta
+
+
+def conv_roll(proj: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slots: torch.Tensor, n_seqs: int, channels: int) -> None:
+    """Moves every sequence's convolution state ``[slots, taps - 1, channels]`` on by the step's inputs (the first
+    ``channels`` columns of ``proj``)."""
+    _check(proj, "proj", dims=2)
+    _check(state, "state", torch.float32, 3)
+    call("gk_conv_roll", ptr(proj), dtype_code(proj.dtype), proj.shape[1], ptr(state), ptr(cu_q), ptr(slots), n_seqs, channels,
+         state.shape[1] + 1, stream_ptr())
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+               cu_q: torch.Tensor, slots: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    """The recurrence ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` over the step's tokens of every
+    sequence, from and to ``state [slots, n_heads, d, dv]`` (32-bit).  Returns ``o [T, n_heads, dv]`` (32-bit)."""
+    require_device(q.device)
+    for name, t in (("q", q), ("k", k), ("v", v), ("g", g)):
+        _check(t, name, torch.float32, 3)
+    _check(beta, "beta", torch.float32, 2)
+    _check(state, "state", torch.float32, 4)
+    T, n_kv, d = q.shape
+    n_heads, dv = v.shape[1], v.shape[2]
+    if tuple(state.shape[1:]) != (n_heads, d, dv) or tuple(g.shape) != (T, n_heads, d) or k.shape != q.shape:
+        raise KernelError("delta_scan: the state or the inputs have other sizes than the heads")
+    out = torch.empty((T, n_heads, dv), dtype=torch.float32, device=q.device)
+    call("gk_delta_scan", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(state), ptr(out), ptr(cu_q), ptr(slots), n_seqs, n_heads,
+         n_kv, d, dv, stream_ptr())
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, gate_at: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``o [T, H, dv]`` (32-bit) divided by each head's root mean square, times ``weight [dv]``, times the sigmoid of
+    ``gate[:, gate_at : gate_at + H dv]``.  Returns ``[T, H dv]`` in ``out_dtype``."""
+    _check(o, "o", torch.float32, 3)
+    _check(weight, "weight", torch.float32, 1)
+    _check(gate, "gate", dims=2)
+    T, H, dv = o.shape
+    if gate.shape[1] < gate_at + H * dv or weight.shape[0] != dv:
+        raise KernelError("head_norm_gate: gate or weight do not fit the heads")
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    call("gk_head_norm_gate", ptr(o), ptr(weight), gate.data_ptr() + gate_at * gate.element_size(), dtype_code(gate.dtype),
+         gate.shape[1], ptr(out), dtype_code(out_dtype), T, H, dv, float(eps), stream_ptr())
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+def route_groups(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, top: int, n_groups: int, keep: int,
+                 scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """Chosen experts ``[T, top]`` (int32) and their weights (float32): sigmoid scores, choice by score plus
+    ``correction`` among the experts of the best ``keep`` of ``n_groups`` groups, weight = score times ``scale``."""
+    require_device(h.device)
+    _check(h, "h", dims=2)
+    _check(w_router, "w_router", torch.float32, 2)
+    _check(correction, "correction", torch.float32, 1)
+    T, width = h.shape
+    n_experts = w_router.shape[0]
+    if w_router.shape[1] != width or correction.shape[0] != n_experts:
+        raise KernelError("route_groups: router sizes do not fit")
+    ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    call("gk_route_groups", ptr(h), dtype_code(h.dtype), ptr(w_router), ptr(correction), ptr(ids), ptr(weights), T, width, n_experts,
+         top, n_groups, keep, float(scale), stream_ptr())
+    return ids, weights
+
+
+def experts_pairwise(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                     add: torch.Tensor | None = None) -> torch.Tensor:
+    """``add + sum_k weights[t, k] * down_e(silu(gate_e h_t) * up_e h_t)`` with ``e = ids[t, k]``, a (token, expert) pair
+    at a time.  ``w_gate_up [E, 2, ff, width]``, ``w_down [E, width, ff]``.  Returns 32-bit ``[T, width]``."""
+    require_device(h.device)
+    _check(h, "h", dims=2)
+    _check(w_gate_up, "w_gate_up", dims=4)
+    _check(w_down, "w_down", w_gate_up.dtype, 3)
+    _check(ids, "ids", torch.int32, 2)
+    _check(weights, "weights", torch.float32, 2)
+    T, width = h.shape
+    E, _, ff, _ = w_gate_up.shape
+    top = ids.shape[1]
+    if tuple(w_gate_up.shape) != (E, 2, ff, width) or tuple(w_down.shape) != (E, width, ff):
+        raise KernelError("experts: weight shapes do not fit")
+    if add is not None:
+        _check(add, "add", h.dtype, 2)
+    act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    out = torch.empty((T, width), dtype=torch.float32, device=h.device)
+    call("gk_experts_up", ptr(h), dtype_code(h.dtype), ptr(w_gate_up), dtype_code(w_gate_up.dtype), ptr(ids), ptr(act), T, width, ff,
+         top, stream_ptr())
+    call("gk_experts_down", ptr(act), dtype_code(h.dtype), ptr(w_down), dtype_code(w_down.dtype), ptr(ids), ptr(weights), ptr(add),
+         ptr(out), T, width, ff, top, stream_ptr())
+    return out
+
+
+# ------------------------------------------------------------------ attention with norms over whole projections
+def wide_norm_rope_write(proj: torch.Tensor, n_q: int, n_kv: int, d: int, w_q: torch.Tensor, w_k: torch.Tensor, eps: float,
+                         cos: torch.Tensor | None, sin: torch.Tensor | None, rot: int, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                         slots: torch.Tensor, kv: PagedKV, max_position: int, write_kv: bool = True) -> torch.Tensor:
+    """RMS norm of the whole query row and of the whole key row of every token (``proj [T, >= (n_q + n_kv) d]`` holds
+    q | k), rotation of the first ``rot`` entries of every head, the finished keys into the key pages and the keys as
+    projected into the value pages.  Returns the finished queries ``[T, n_q, d]``."""
+    require_device(proj.device)
+    _check(proj, "proj", dims=2)
+    _check(w_q, "w_q", torch.float32, 1)
+    _check(w_k, "w_k", torch.float32, 1)
+    T = proj.shape[0]
+    if proj.shape[1] < (n_q + n_kv) * d or w_q.shape[0] != n_q * d or w_k.shape[0] != n_kv * d:
+        raise KernelError("wide_norm_rope_write: sizes do not fit")
+    if kv.k.shape[1] != n_kv or kv.k.shape[3] != d or kv.v.shape != kv.k.shape:
+        raise KernelError(f"pages {tuple(kv.k.shape)} do not fit n_kv={n_kv}, head_dim={d}")
+    positions = 0
+    if rot:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError("rotary tables must be [positions, rot / 2]")
+        positions = cos.shape[0]
+    q = torch.empty((T, n_q, d), dtype=proj.dtype, device=proj.device)
+    call("gk_wide_norm_rope_write", ptr(proj), dtype_code(proj.dtype), proj.shape[1], ptr(w_q), ptr(w_k), ptr(cos) if rot else None,
+         ptr(sin) if rot else None, positions, ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(kv.block_table), ptr(q),
+         ptr(kv.k) if write_kv else None, ptr(kv.v) if write_kv else None, dtype_code(kv.k.dtype), T, n_q, n_kv, d, int(rot),
+         kv.max_pages, kv.page_size, float(eps), int(max_position), stream_ptr())
+    return q
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, gate_at: int) -> torch.Tensor:
+    """``o [T, n] * sigmoid(gate[:, gate_at : gate_at + n])``."""
+    _check(o, "o", dims=2)
+    _check(gate, "gate", o.dtype, 2)
+    T, n = o.shape
+    if gate.shape[1] < gate_at + n or gate.shape[0] != T:
+        raise KernelError("sigmoid_gate: the gate is narrower than the rows")
+    out = torch.empty_like(o)
+    call("gk_sigmoid_gate", ptr(o), gate.data_ptr() + gate_at * gate.element_size(), gate.shape[1], ptr(out), dtype_code(o.dtype), T, n,
+         stream_ptr())
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x <- cap * tanh(x / cap)`` in place (32-bit)."""
+    _check(x, "x", torch.float32)
+    call("gk_softcap", ptr(x), x.numel(), float(cap), stream_ptr())
+    return x

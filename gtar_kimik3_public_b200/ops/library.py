@@ -29,7 +29,7 @@ _lib: ctypes.CDLL | None = None
 P, I, L, F, U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
 
 _SIGNATURES: dict[str, list] = {
-    "gk_embed_rows": [P, I, P, P, I, I, P],
+    "gk_embed_rows": [P, I, P, P, I, I, F, P],
     "gk_add_rmsnorm": [P, P, I, P, I, P, I, P, I, I, F, P],
     "gk_swiglu": [P, P, I, I, I, I, P],
     "gk_decode_layers_plan": [I, I, I, I, I, I, I, I, P],
@@ -45,7 +45,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_latent_prepare": [P, I, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
     "gk_attention_latent_tiled": [P, L, L, P, I, I, P, P, P, P, L, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_latent_exact": [P, L, L, P, I, I, P, P, P, P, L, L, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
-    "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, I, I, P, P],
     "gk_gemm_bf16_tc_qkv": [P, I, P, I, I, I, I, P, P, I, I, F, P, P, I, I, P, P, P, P, I, I, P, P, P, P, P],
@@ -66,6 +66,16 @@ _SIGNATURES: dict[str, list] = {
     "gk_set_attention_prefill_stay": [I],
     "gk_argmax": [P, L, I, I, P, I, P, P],
     "gk_sample": [P, L, I, I, F, I, U, P, P, I, P, I, P, P],
+    "gk_delta_prepare": [P, I, L, P, I, L, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "gk_conv_roll": [P, I, L, P, P, P, I, I, I, P],
+    "gk_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "gk_head_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, P],
+    "gk_route_groups": [P, I, P, P, P, P, I, I, I, I, I, I, F, P],
+    "gk_experts_up": [P, I, P, I, P, P, I, I, I, I, P],
+    "gk_experts_down": [P, I, P, I, P, P, P, P, I, I, I, I, P],
+    "gk_wide_norm_rope_write": [P, I, L, P, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "gk_sigmoid_gate": [P, P, L, P, I, L, I, P],
+    "gk_softcap": [P, L, F, P],
 }
 
 

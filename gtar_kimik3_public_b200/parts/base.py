@@ -37,6 +37,9 @@ class TensorSpec:
     optional: bool = False
     # (mean, standard deviation) that the random-weights mode draws the tensor with; None: the mode's rule for the kind
     init: tuple[float, float] | None = None
+    # dimensions (indices into ``shape``) whose size the model file chooses: ``shape`` then holds the size that the
+    # random-weights mode writes, and the part reads the real one off the tensor when it loads
+    free: tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)

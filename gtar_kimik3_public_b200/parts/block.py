@@ -88,6 +88,45 @@ class PreNormBlock(Block):
 register_part("block", "pre_norm", PreNormBlock)
 
 
+class ParallelBlock(Block):
+    """A layer whose two branches read ONE norm: ``n = norm(x); x += mixer(n) + feed_forward(n)`` (the feed-forward may be
+    absent).  The sum of the two branches is formed in 32-bit and handed on as ``pending``, so that the add into the
+    stream happens inside the next norm."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, feed_forward: FeedForward | None, names: dict[str, str] | None = None):
+        self.norm, self.mixer, self.feed_forward = norm, mixer, feed_forward
+        self.names = {"norm": "", "mixer": "mix.", "feed_forward": "mlp.", **(names or {})}
+
+    def children(self):
+        parts = [(self.names["norm"], self.norm), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            parts.append((self.names["feed_forward"], self.feed_forward))
+        return parts
+
+    def tensor_specs(self):
+        return {prefix + name: spec for prefix, part in self.children() for name, spec in part.tensor_specs().items()}
+
+    def load(self, tensors):
+        for prefix, part in self.children():
+            part.load({name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors})
+
+    def weight_bytes(self):
+        return sum(part.weight_bytes() for _, part in self.children())
+
+    def forward(self, h, pending, ctx: StepContext, cache):
+        x = self.norm.forward(h, pending, ctx.dtype)
+        branch = self.mixer.forward(x, ctx, cache)
+        if self.feed_forward is None:
+            return h, branch
+        added = getattr(self.feed_forward, "forward_added", None)
+        if added is not None:
+            return h, added(x, ctx, branch)
+        return h, branch.float() + self.feed_forward.forward(x, ctx).float()
+
+
+register_part("block", "parallel", ParallelBlock)
+
+
 class SandwichBlock(Block):
     """A layer that norms every branch before AND after it, scales it per channel, passes the mixer's input
     through a short causal convolution over time, and mixes the results of all earlier layers into what it hands on:

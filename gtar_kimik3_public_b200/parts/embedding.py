@@ -13,9 +13,10 @@ from .base import Part, TensorSpec
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight", scale: float = 1.0):
+        """``scale`` multiplies every row as it enters the 32-bit stream (1.0: the table's rows as they are)."""
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
-        self.weight_name = weight_name
+        self.weight_name, self.scale = weight_name, float(scale)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self):
@@ -25,26 +26,29 @@ class TokenEmbedding(Part):
         self.weight = tensors[self.weight_name].contiguous()
 
     def forward(self, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        return F.embed_rows(self.weight, ids, out)
+        return F.embed_rows(self.weight, ids, out, self.scale)
 
 
 class OutputHead(Part):
     graph_safe = True
 
-    """Logits in float32.  ``tied_to`` names an embedding whose table is used instead of an own matrix."""
+    """Logits in float32.  ``tied_to`` names an embedding whose table is used instead of an own matrix.  ``softcap``:
+    the logits become ``softcap * tanh(logits / softcap)`` (None: they stay as they are)."""
 
-    def __init__(self, hidden_size: int, vocab_size: int, tied_to: TokenEmbedding | None = None):
+    def __init__(self, hidden_size: int, vocab_size: int, tied_to: TokenEmbedding | None = None, weight_name: str = "weight",
+                 softcap: float | None = None):
         self.hidden_size, self.vocab_size, self.tied_to = int(hidden_size), int(vocab_size), tied_to
+        self.weight_name, self.softcap = weight_name, (None if softcap is None else float(softcap))
         self._weight: torch.Tensor | None = None
 
     def tensor_specs(self):
         # A tied model's file may still carry the head (the reference's state dict does): it is
         # accepted and not read.
-        return {"weight": TensorSpec((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
+        return {self.weight_name: TensorSpec((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
 
     def load(self, tensors):
         if self.tied_to is None:
-            self._weight = tensors["weight"].contiguous()
+            self._weight = tensors[self.weight_name].contiguous()
 
     @property
     def weight(self) -> torch.Tensor:
@@ -54,4 +58,5 @@ class OutputHead(Part):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
-        return linear(z, self.weight, torch.float32)
+        logits = linear(z, self.weight, torch.float32)
+        return F.softcap_(logits, self.softcap) if self.softcap is not None else logits

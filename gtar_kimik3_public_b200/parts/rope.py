@@ -18,11 +18,14 @@ from .base import PositionEncoding, register_part
 class RotaryEncoding(PositionEncoding):
     graph_safe = True
 
-    def __init__(self, dim: int, base: float):
+    def __init__(self, dim: int, base: float, precise: bool = False):
+        """``precise``: frequencies, angles, cosines and sines are formed in 64-bit and rounded once to the 32-bit
+        tables (the default forms them in 32-bit, as the reference does)."""
         if dim % 2:
             raise ValueError(f"rotary dimension must be even, got {dim}")
         self.dim = int(dim)
         self.base = float(base)
+        self.precise = bool(precise)
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
         self._replaced: list[torch.Tensor] = []  # shorter tables of before: captured launches may still read them
@@ -43,6 +46,12 @@ class RotaryEncoding(PositionEncoding):
             # on its position only), so they are kept instead of freed.
             self._replaced += [self.cos, self.sin]
         n = max(max_position + 1, 2 * have, 64)
+        if self.precise:
+            inv = self.base ** (-torch.arange(0, self.dim, 2, dtype=torch.float64) / self.dim)
+            freqs = torch.arange(n, dtype=torch.float64)[:, None] * inv[None, :]
+            self.cos = (freqs.cos() * self.magnitude()).float().to(device).contiguous()
+            self.sin = (freqs.sin() * self.magnitude()).float().to(device).contiguous()
+            return
         positions = torch.arange(n, dtype=torch.float32, device=device)
         freqs = positions[:, None] * self.inv_freq().to(device)[None, :]
         magnitude = self.magnitude()

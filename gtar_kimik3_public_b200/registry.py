@@ -72,3 +72,7 @@ def _ensure_builtin() -> None:
     from .models.dasusun import build_dasusun_plan
 
     register_architecture(DasusunConfig.ARCH_NAMES, DasusunConfig, build_dasusun_plan)
+    from .config.pofadra import PofadraConfig
+    from .models.pofadra import build_pofadra_plan
+
+    register_architecture(PofadraConfig.ARCH_NAMES, PofadraConfig, build_pofadra_plan)

@@ -53,7 +53,10 @@ class WeightsError(ValueError):
 def check_tensors(folder, specs: dict[str, TensorSpec], have_shapes: dict[str, tuple], have_dtypes: dict[str, torch.dtype]) -> None:
     missing = [n for n, s in specs.items() if n not in have_shapes and not s.optional]
     unexpected = [n for n in have_shapes if n not in specs]
-    wrong_shape = [(n, have_shapes[n], s.shape) for n, s in specs.items() if n in have_shapes and tuple(have_shapes[n]) != tuple(s.shape)]
+    def fits(have, spec):
+        return len(have) == len(spec.shape) and all(a == b or i in spec.free for i, (a, b) in enumerate(zip(have, spec.shape)))
+
+    wrong_shape = [(n, have_shapes[n], s.shape) for n, s in specs.items() if n in have_shapes and not fits(tuple(have_shapes[n]), s)]
     wrong_kind = []
     for name, spec in specs.items():
         if name not in have_dtypes:
