@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int* __restrict__ kv_len, const int* __restrict__ slots,
     const int* __restrict__ block_table, int n_q, int n_kv, int max_pages, float sl2, int window, int n_splits,
-    int cluster_merge, int group, const FusedQkv fused) {  // group = n_q / n_kv, divided on the host
+    int cluster_merge, int group, int sink, const FusedQkv fused) {  // group = n_q / n_kv, divided on the host
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DecodeSmem<D>& sm = *reinterpret_cast<DecodeSmem<D>*>(smem_raw);
     const int split = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
@@ -354,6 +354,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
         }
         const int hq = hk * group + r;
         if (n_splits == 1) {
+            if (sink) ll += exp2_fast(-mm);  // one more term in the denominator: a key of score 0 without a value
             out[((size_t)seq * n_q + hq) * D + c] = __float2bfloat16_rn(__fdividef(acc, ll));
         } else if (cluster_merge) {
             // The splits of one (sequence, kv head) are one cluster: a block sends each of its partial outputs
@@ -411,6 +412,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
                     ll += ls[sp] * f;
                     acc += os[sp] * f;
                 }
+            if (sink) ll += exp2_fast(-mm);
             out[((size_t)seq * n_q + hk * group + r) * D + (idx % D)] = __float2bfloat16_rn(__fdividef(acc, ll));
         }
     }
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(
 // out[seq, head, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s
 template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              __nv_bfloat16* __restrict__ out, int n_splits) {
+                                              __nv_bfloat16* __restrict__ out, int n_splits, int sink) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t row = blockIdx.x;  // seq * n_q + head
@@ -429,6 +431,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
     float ll = 0.f;
     for (int s = 0; s < n_splits; ++s)
         if (ml[2 * s] != -INFINITY) ll += ml[2 * s + 1] * exp2f(ml[2 * s] - mm);
+    if (sink) ll += exp2f(-mm);
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < n_splits; ++s)
@@ -440,7 +443,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 template <int D>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml,
                   const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
-                  int max_pages, float scale, int window, int n_splits, cudaStream_t stream, const FusedQkv& fused) {
+                  int max_pages, float scale, int window, int n_splits, cudaStream_t stream, const FusedQkv& fused, int sink = 0) {
     const size_t stage_bytes = sizeof(DecodeSmem<D>);
     const size_t merge_bytes = (size_t)WARPS * 16 * (D + 2) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -458,11 +461,11 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     gk_launch_cluster(attention_decode_kernel<D>, grid, dim3(WARPS * 32), smem, stream,
         dim3(cluster_merge ? n_splits : 1, 1, 1),
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out,
-        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge, n_q / n_kv, fused);
+        part_o, part_ml, kv_len, slots, block_table, n_q, n_kv, max_pages, sl2, window, n_splits, cluster_merge, n_q / n_kv, sink, fused);
     GK_CHECK_LAUNCH("attention_decode");
     if (n_splits > 1 && !cluster_merge) {
         gk_launch(attention_decode_merge_kernel<D>, dim3(n_seqs * n_q), dim3(D <= 64 ? 64 : 128), 0, stream,
-                  (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
+                  (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sink);
         GK_CHECK_LAUNCH("attention_decode_merge");
     }
     return GK_OK;
@@ -477,7 +480,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
 static int decode_entry(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml,
                         const int* kv_len, const int* slots, const int* block_table, int n_seqs, int n_q, int n_kv,
                         int head_dim, int max_pages, int page_size, float scale, int window, int n_splits, void* stream,
-                        const FusedQkv& fused) {
+                        const FusedQkv& fused, int sink = 0) {
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(n_q / n_kv <= 16, "attention_decode: groups of more than 16 query heads per kv head are not supported");
     GK_REQUIRE(page_size == attn::PAGE, "attention_decode: page_size must be %d, got %d", attn::PAGE, page_size);
@@ -490,19 +493,19 @@ static int decode_entry(const void* q, const void* k_pages, const void* v_pages,
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
         return launch_decode<64>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
-                                 max_pages, scale, window, n_splits, s, fused);
+                                 max_pages, scale, window, n_splits, s, fused, sink);
     return launch_decode<128>(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv,
-                              max_pages, scale, window, n_splits, s, fused);
+                              max_pages, scale, window, n_splits, s, fused, sink);
 }
 
 GK_EXPORT int gk_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                        float* part_o, float* part_ml, const int* kv_len, const int* slots,
                                        const int* block_table, int n_seqs, int n_q, int n_kv, int head_dim,
                                        int max_pages, int page_size, float scale, int window, int n_splits,
-                                       void* stream) {
+                                       int sink, void* stream) {
     FusedQkv none = {};
     return decode_entry(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q, n_kv, head_dim,
-                        max_pages, page_size, scale, window, n_splits, stream, none);
+                        max_pages, page_size, scale, window, n_splits, stream, none, sink);
 }
 
 // Decode attention that also does the step before it: `qkv` is the packed projection of each sequence's
@@ -572,7 +575,7 @@ GK_EXPORT int gk_attention_decode_bf16_no_alloc(const void* q, const void* k_pag
     float* part_o = g_no_alloc_ptr[device];
     float* part_ml = part_o + (size_t)n_seqs * n_q * n_splits * head_dim;
     return gk_attention_decode_bf16(q, k_pages, v_pages, out, part_o, part_ml, kv_len, slots, block_table, n_seqs, n_q,
-                                    n_kv, head_dim, max_pages, page_size, scale, window, n_splits, stream);
+                                    n_kv, head_dim, max_pages, page_size, scale, window, n_splits, 0, stream);
 }
 
 // How many clusters of `cluster` blocks of the decode attention kernel the device holds at once (blocks for a cluster

@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
     const int* __restrict__ kv_len, const int* __restrict__ slots, const int* __restrict__ block_table, int n_q,
-    int n_kv, int max_pages, float sl2, int window) {
+    int n_kv, int max_pages, float sl2, int window, int sink) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     PrefillSmem<D>& sm = *reinterpret_cast<PrefillSmem<D>*>(smem_raw);
     pdl_launch_dependents();
@@ -151,7 +151,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(
     for (int h = 0; h < 2; ++h) {
         if (!row_ok[h]) continue;
         const int r = wrow0 + (lane >> 2) + 8 * h;
-        const float inv = 1.0f / l[h];
+        // with a sink the denominator has one more term: a key of score 0 that has no value
+        const float inv = 1.0f / (sink ? l[h] + exp2_fast(-m[h]) : l[h]);
         __nv_bfloat16* orow = out + ((size_t)(q_begin + tok[h]) * n_q + (size_t)hk * group + (r % group)) * D;
 #pragma unroll
         for (int j = 0; j < D / 8; ++j)
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(
 template <int D>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q, const int* kv_len,
                    const int* slots, const int* block_table, int n_seqs, int max_q_len, int n_q, int n_kv, int max_pages,
-                   float scale, int window, cudaStream_t stream) {
+                   float scale, int window, int sink, cudaStream_t stream) {
     const size_t smem = sizeof(PrefillSmem<D>);
     static bool configured = false;
     if (!configured) {
@@ -176,7 +177,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
     dim3 grid((unsigned)blocks, n_kv, n_seqs);
     gk_launch(attention_prefill_kernel<D>, grid, dim3(PF_WARPS * 32), smem, stream, (const __nv_bfloat16*)q,
               (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, cu_q, kv_len, slots,
-              block_table, n_q, n_kv, max_pages, scale * 1.4426950408889634f, window);
+              block_table, n_q, n_kv, max_pages, scale * 1.4426950408889634f, window, sink);
     GK_CHECK_LAUNCH("attention_prefill");
     return GK_OK;
 }
@@ -189,7 +190,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
 GK_EXPORT int gk_attention_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                         const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
                                         int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
-                                        int page_size, float scale, int window, void* stream) {
+                                        int page_size, float scale, int window, int sink, void* stream) {
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(page_size == attn::PAGE, "attention_prefill: page_size must be %d, got %d", attn::PAGE, page_size);
     GK_REQUIRE(head_dim == 64 || head_dim == 128, "attention_prefill: head_dim %d is not 64 or 128 (use the exact kernel)", head_dim);
@@ -199,7 +200,7 @@ GK_EXPORT int gk_attention_prefill_bf16(const void* q, const void* k_pages, cons
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
         return launch_prefill<64>(q, k_pages, v_pages, out, cu_q, kv_len, slots, block_table, n_seqs, max_q_len, n_q, n_kv,
-                                  max_pages, scale, window, s);
+                                  max_pages, scale, window, sink, s);
     return launch_prefill<128>(q, k_pages, v_pages, out, cu_q, kv_len, slots, block_table, n_seqs, max_q_len, n_q, n_kv,
-                               max_pages, scale, window, s);
+                               max_pages, scale, window, sink, s);
 }

@@ -57,18 +57,16 @@ def paged_attention(q: torch.Tensor, kv: F.PagedKV, ctx, scale: float, window: i
     softmax's denominator (a key of score 0 without a value)."""
     n_q, d = q.shape[1], q.shape[2]
     n_kv = kv.k.shape[1]
-    if sink:
-        return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window, sink=True)
     fast = q.dtype == torch.bfloat16 and d in FAST_HEAD_DIMS and kv.page_size == 64 and n_q // n_kv <= 16
     if fast and ctx.all_single:
-        if decode_flat_preferred(ctx, n_kv, kv):
+        if not sink and decode_flat_preferred(ctx, n_kv, kv):
             return F.attention_decode_flat(q, None, n_q, n_kv, d, None, None, 1.0, None, None, kv, ctx.kv_len, ctx.slots,
                                            ctx.max_position, scale, window)
         splits = decode_split_count(ctx, n_kv, kv)
-        return F.attention_decode(q, kv, ctx.kv_len, ctx.slots, scale, window, splits)
+        return F.attention_decode(q, kv, ctx.kv_len, ctx.slots, scale, window, splits, sink=sink)
     if fast:
-        return F.attention_prefill(q, kv, ctx.cu_q, ctx.kv_len, ctx.slots, ctx.max_q_len, scale, window)
-    return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window)
+        return F.attention_prefill(q, kv, ctx.cu_q, ctx.kv_len, ctx.slots, ctx.max_q_len, scale, window, sink=sink)
+    return F.attention_exact(q, kv, ctx.tok_pos, ctx.tok_seq, ctx.slots, scale, window, sink=sink)
 
 
 # "0" sends bfloat16 latent attention through the exact kernel too (for measurements and for telling the kernels apart)

@@ -645,8 +645,10 @@ def attention_decode(
     n_splits: int = 1,
     out: torch.Tensor | None = None,
     use_scratch: bool = False,
+    sink: bool = False,
 ) -> torch.Tensor:
-    """Attention of one new token per sequence (``q [n_seqs, n_q, d]`` bfloat16, ``d`` 64 or 128) over
+    """(``sink``: one more term in the softmax's denominator, a key of score 0 without a value.)
+    Attention of one new token per sequence (``q [n_seqs, n_q, d]`` bfloat16, ``d`` 64 or 128) over
     the pages; ``kv_len[i]`` counts the sequence's cached tokens including the new one.  Up to eight
     splits merge inside one kernel (a cluster per sequence and kv head); more, or ``use_scratch``, go
     through scratch memory allocated here and a second kernel."""
@@ -671,7 +673,7 @@ def attention_decode(
     call(
         "gk_attention_decode_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(part_o), ptr(part_ml), ptr(kv_len),
         ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),
-        int(n_splits), stream_ptr(),
+        int(n_splits), int(sink), stream_ptr(),
     )
     return out
 
@@ -834,11 +836,13 @@ def attention_prefill(
     window: int = 0,
     out: torch.Tensor | None = None,
     tensor_cores: str = "auto",
+    sink: bool = False,
 ) -> torch.Tensor:
     """Causal attention of the packed new tokens ``q [n_tokens, n_q, d]`` (bfloat16, ``d`` 64 or 128) of
     ``n_seqs`` sequences over the pages.  Sequence ``i`` owns tokens ``cu_q[i] .. cu_q[i+1]-1``, which
     are its last positions: ``kv_len[i]`` counts its cached tokens including them.  ``tensor_cores``:
-    ``"tcgen05"`` (head size 128 only), ``"mma"`` (the warp-level kernel), or ``"auto"``."""
+    ``"tcgen05"`` (head size 128 only), ``"mma"`` (the warp-level kernel), or ``"auto"``.  ``sink``: one more term in
+    the softmax's denominator, a key of score 0 without a value (the warp-level kernel has it)."""
     require_device(q.device)
     _check(q, "q", torch.bfloat16, 3)
     n, n_q, d = q.shape
@@ -858,7 +862,9 @@ def attention_prefill(
         raise KernelError(f"tensor_cores must be auto, tcgen05 or mma, got {tensor_cores!r}")
     if tensor_cores == "tcgen05" and d != 128:
         raise KernelError("the tcgen05 prefill attention takes head size 128 only")
-    if tensor_cores == "tcgen05" or (tensor_cores == "auto" and d == 128):
+    if sink and tensor_cores == "tcgen05":
+        raise KernelError("the tcgen05 prefill attention has no sink")
+    if not sink and (tensor_cores == "tcgen05" or (tensor_cores == "auto" and d == 128)):
         call(
             "gk_attention_prefill_tc_tokens_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
             ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, kv.k.shape[0],
@@ -868,7 +874,7 @@ def attention_prefill(
     call(
         "gk_attention_prefill_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
         ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, float(scale), int(window),
-        stream_ptr(),
+        int(sink), stream_ptr(),
     )
     return out
 

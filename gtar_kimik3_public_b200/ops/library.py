@@ -46,7 +46,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_attention_latent_tiled": [P, L, L, P, I, I, P, P, P, P, L, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_latent_exact": [P, L, L, P, I, I, P, P, P, P, L, L, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "gk_attention_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
-    "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "gk_attention_decode_bf16": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "gk_gemm_bf16_tc": [P, I, L, P, I, L, I, P, I, L, L, I, I, I, I, I, P, P],
     "gk_gemm_bf16_tc_qkv": [P, I, P, I, I, I, I, P, P, I, I, F, P, P, I, I, P, P, P, P, I, I, P, P, P, P, P],
     "gk_gemv_bf16": [P, I, I, L, P, I, L, P, I, I, P],
@@ -60,7 +60,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_attention_decode_flat_bf16": [P, P, P, P, I, I, F, P, P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_decode_flat_resident_blocks": [I],
     "gk_attention_decode_bf16_no_alloc": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
-    "gk_attention_prefill_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    "gk_attention_prefill_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_prefill_tc_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P],
     "gk_attention_prefill_tc_tokens_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P, L],
     "gk_set_attention_prefill_stay": [I],

@@ -169,7 +169,7 @@ def forward(tokens: torch.Tensor, weights: dict, config: dict, dtype=torch.float
     """Logits [T, vocab] of one sequence.  ``keep_layers``: a list that receives the stream after every layer."""
     w = {name: (t.to(dtype) if t.is_floating_point() else t) for name, t in weights.items()}
     eps = config["norm"]["eps"]
-    x = w["embed"][tokens] * config["embedding"]["scale"]
+    x = w["embed"][tokens] * (config.get("embedding") or {"scale": 1.0})["scale"]
     for i, layer in enumerate(config["layers"]):
         h = rms(x, eps) * w[f"l{i}.norm1"]
         branch = MIXERS[layer["type"]](h, w, f"l{i}.mix.", layer["mixer"], eps)
