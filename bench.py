@@ -14,7 +14,7 @@ Weights are random (written as a model folder by the library's random-weights mo
 from there), token ids are seeded uniform-random: there is no network for checkpoints or data.
 The library runs on one GPU; with --gpus N > 1 a line says so and the exit code is 2.
 
-``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
+``--compare pofadra`` does the same for the Pofadra decoder.  ``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
 at equal layer sizes (prefill and decode throughput of both, and the new design's kernels one by one against their rooflines).
 """
 
@@ -812,6 +812,205 @@ def run_compare(args) -> dict:
             "results": results}
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --compare pofadra: the Pofadra decoder (delta-rule layers with one windowed attention layer in four, routed experts)
+# beside the dense transformer at equal width and equal bytes of weights read per token, and its kernels one by one.
+def _pofadra_config(width, layers, heads, kv_heads, dim, vdim, conv, rank, a_heads, a_kv, a_dim, window, rot, experts, top, ff,
+                    groups, keep, vocab):
+    delta = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "decay_rank": rank, "gate_rank": rank}
+    attention = {"heads": a_heads, "kv_heads": a_kv, "dim": a_dim, "vdim": a_dim, "scale": a_dim ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 10000.0, "dims": rot}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": groups, "keep": keep}}}
+    stack = [{"type": "attention" if i % 4 == 3 else "channel_delta", "mixer": attention if i % 4 == 3 else delta, "mlp": mlp}
+             for i in range(layers)]
+    return {"architecture": "Pofadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_softcap": 30.0, "layers": stack, "initializer_range": 0.02, "max_position_embeddings": 4096}
+
+
+POFADRA_SIZES = {
+    # name: (Pofadra sizes, transformer sizes); 8 layers each, vocabulary 32,768; a token's experts hold what the dense
+    # feed-forward of the transformer beside it holds (top * expert ff = the dense ff)
+    "width1024": (dict(width=1024, layers=8, heads=8, kv_heads=8, dim=128, vdim=128, conv=4, rank=64, a_heads=16, a_kv=4, a_dim=64,
+                       window=1024, rot=32, experts=32, top=4, ff=768, groups=4, keep=2, vocab=32768),
+                  dict(hidden=1024, layers=8, heads=16, kv_heads=8, head_dim=128, ff=3072, vocab=32768)),
+    "width2048": (dict(width=2048, layers=8, heads=16, kv_heads=16, dim=128, vdim=128, conv=4, rank=128, a_heads=16, a_kv=4, a_dim=128,
+                       window=2048, rot=64, experts=64, top=6, ff=1024, groups=8, keep=4, vocab=32768),
+                  dict(hidden=2048, layers=8, heads=16, kv_heads=8, head_dim=128, ff=6144, vocab=32768)),
+}
+
+
+def _pofadra_prefill_flops(d: dict, tokens: int) -> float:
+    w, H, G, dk, dv = d["width"], d["heads"], d["kv_heads"], d["dim"], d["vdim"]
+    n_attn = d["layers"] // 4
+    n_delta = d["layers"] - n_attn
+    delta = 2 * (w * (2 * G * dk + H * dv + H + 2 * d["rank"]) + 2 * d["rank"] * H * (dk + dv) // 2 + H * dv * w) + H * dv * 6 * dk
+    aq, ak, ad = d["a_heads"], d["a_kv"], d["a_dim"]
+    seen = sum(min(t + 1, d["window"]) for t in range(tokens))
+    attention = 2 * w * ((2 * aq + ak) * ad) + 2 * aq * ad * w
+    experts = 2 * w * d["experts"] + d["top"] * 6 * w * d["ff"]
+    return (n_delta * delta + n_attn * attention + d["layers"] * experts) * tokens + n_attn * aq * seen * 4 * ad + 2 * w * d["vocab"]
+
+
+def _pofadra_kernel_table(d: dict, t: dict, peak: dict) -> dict:
+    """The new design's kernels alone and the like kernels of the transformer, each with its share of its roofline."""
+    import torch
+
+    from gtar_kimik3_public_b200.ops import functional as F
+    from gtar_kimik3_public_b200.ops.linear import linear_grouped
+
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(48 << 20, dtype=torch.float32, device=dev)  # 192 MB: larger than the 126 MB L2
+    hbm, tflops = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+    out = {}
+
+    def record(name, ms, n_bytes, flops=0.0):
+        floor = max(n_bytes / hbm, flops / tflops) * 1e3
+        out[name] = {"us": round(ms * 1e3, 2), "roofline_us": round(floor * 1e3, 2), "frac": round(floor / ms, 4),
+                     "bound": "hbm" if n_bytes / hbm >= flops / tflops else "tensor"}
+
+    w, H, G, dk, dv, taps = d["width"], d["heads"], d["kv_heads"], d["dim"], d["vdim"], d["conv"]
+    aq, ak, ad, window = d["a_heads"], d["a_kv"], d["a_dim"], d["window"]
+    E, top, ff = d["experts"], d["top"], d["ff"]
+    C = 2 * G * dk + H * dv
+    for label, tokens, n_seqs in (("prefill_2048", 2048, 1), ("decode_b8_ctx2048", 8, 8)):
+        each = tokens // n_seqs
+        inner = 1 if n_seqs == 1 else 20
+        past = 0 if n_seqs == 1 else 2047
+        length = past + each
+        pages_each = -(-length // 64)
+        table = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).view(n_seqs, pages_each)
+        tok_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each)
+        tok_pos = (torch.arange(each, dtype=torch.int32, device=dev) + past).repeat(n_seqs)
+        cu_q = torch.arange(n_seqs + 1, dtype=torch.int32, device=dev) * each
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        kv_len = torch.full((n_seqs,), length, dtype=torch.int32, device=dev)
+        # ---- the delta rule
+        proj = (torch.randn(tokens, C + H + (-(C + H)) % 8, device=dev) * 0.5).bfloat16()
+        low = torch.randn(tokens, H * (dk + dv), device=dev)
+        conv_w, conv_state = torch.randn(C, taps, device=dev) * 0.3, torch.zeros(n_seqs, taps - 1, C, device=dev)
+        a_log, dt_bias = torch.randn(H, device=dev) - 1, torch.randn(H * dk, device=dev) - 1
+        ms = _event_ms(lambda: F.delta_prepare(proj, low, conv_w, conv_state, a_log, dt_bias, tok_pos, tok_seq, cu_q, slots, H, G, dk, dv, taps),
+                       flush=flush, inner=inner)
+        record(f"pofadra convolutions, unit lengths, decays and beta, {label}", ms, tokens * (2 * (C + H) + 4 * H * dk + 4 * (C + H * dk + H)))
+        q, k, v, g, beta = F.delta_prepare(proj, low, conv_w, conv_state, a_log, dt_bias, tok_pos, tok_seq, cu_q, slots, H, G, dk, dv, taps)
+        state = torch.zeros(n_seqs, H, dk, dv, device=dev)
+        ms = _event_ms(lambda: F.delta_scan(q, k, v, g, beta, state, cu_q, slots, n_seqs), flush=flush, inner=inner)
+        record(f"pofadra delta rule recurrence, {label}", ms, 4 * (tokens * (2 * G * dk + H * dk + 2 * H * dv + H) + 2 * n_seqs * H * dk * dv))
+        o = torch.randn(tokens, H, dv, device=dev)
+        norm_w = torch.ones(dv, device=dev)
+        ms = _event_ms(lambda: F.head_norm_gate(o, norm_w, low, H * dk, 1e-6, torch.bfloat16), flush=flush, inner=inner)
+        record(f"pofadra head norm and gate, {label}", ms, tokens * H * dv * (4 + 4 + 2))
+        # ---- attention with wide norms and a sink, beside the transformer's
+        kv = F.PagedKV(torch.randn(n_seqs * pages_each, ak, 64, ad, device=dev).bfloat16() * 0.1,
+                       torch.randn(n_seqs * pages_each, ak, 64, ad, device=dev).bfloat16() * 0.1, table, F.DecodeWork(dev))
+        wide = (torch.randn(tokens, (2 * aq + ak) * ad, device=dev)).bfloat16()
+        angle = torch.arange(length, dtype=torch.float32, device=dev)[:, None] * torch.rand(d["rot"] // 2, device=dev)[None, :]
+        cos, sin = angle.cos().contiguous(), angle.sin().contiguous()
+        wq, wk = torch.ones(aq * ad, device=dev), torch.ones(ak * ad, device=dev)
+        ms = _event_ms(lambda: F.wide_norm_rope_write(wide, aq, ak, ad, wq, wk, 1e-6, cos, sin, d["rot"], tok_pos, tok_seq, slots, kv, length - 1),
+                       flush=flush, inner=inner)
+        record(f"pofadra wide norms, rotation and cache write, {label}", ms, tokens * 2 * ((aq + ak) * ad + aq * ad + 2 * ak * ad))
+        qa = torch.randn(tokens, aq, ad, device=dev).bfloat16()
+        seen = sum(min(p + 1, window) for p in range(past, length)) * n_seqs
+        if n_seqs == 1:
+            ms = _event_ms(lambda: F.attention_prefill(qa, kv, cu_q, kv_len, slots, each, ad ** -0.5, window, sink=True), flush=flush, inner=inner)
+        else:
+            sp = F.decode_splits(n_seqs, ak, length, 64, F.sm_count(dev), F.decode_cluster_places(ad, F.sm_count(dev)))
+            ms = _event_ms(lambda: F.attention_decode(qa, kv, kv_len, slots, ad ** -0.5, window, sp, sink=True), flush=flush, inner=inner)
+        record(f"pofadra window attention with sink, {label}", ms, 2 * (2 * tokens * aq * ad + 2 * n_seqs * min(length, window + each) * ak * ad),
+               4 * aq * ad * seen)
+        gate_src = torch.randn(tokens, aq * ad, device=dev).bfloat16()
+        ms = _event_ms(lambda: F.sigmoid_gate(qa.view(tokens, aq * ad), gate_src, 0), flush=flush, inner=inner)
+        record(f"pofadra output gate, {label}", ms, tokens * aq * ad * 6)
+        # ---- routed experts
+        x = torch.randn(tokens, w, device=dev).bfloat16()
+        router, correction = torch.randn(E, w, device=dev) * 0.05, torch.randn(E, device=dev) * 0.1
+        ms = _event_ms(lambda: F.route_groups(x, router, correction, top, d["groups"], d["keep"], 1.0), flush=flush, inner=inner)
+        record(f"pofadra router, {label}", ms, tokens * w * 2 + E * w * 4)
+        ids, weights = F.route_groups(x, router, correction, top, d["groups"], d["keep"], 1.0)
+        gate_up = (torch.randn(E, 2, ff, w, device=dev) * 0.02).bfloat16()
+        down = (torch.randn(E, w, ff, device=dev) * 0.02).bfloat16()
+        used = int(torch.unique(ids).numel())
+        expert_bytes = used * 3 * ff * w * 2
+        if n_seqs == 1:
+            def grouped():
+                ends, place_of, pair_at = F.experts_sort(ids, E)
+                rows = F.gather_rows(x, pair_at, top)
+                act = F.swiglu(linear_grouped(rows, gate_up.view(E, 2 * ff, w), ends))
+                return F.experts_combine(linear_grouped(act, down, ends), place_of, weights, x)
+            ms = _event_ms(grouped, flush=flush, inner=inner)
+            record(f"pofadra experts (sorted, grouped products), {label}", ms, expert_bytes + tokens * top * (w * 4 + ff * 6), tokens * top * 6 * w * ff)
+        else:
+            ms = _event_ms(lambda: F.experts_pairwise(x, gate_up, down, ids, weights, x), flush=flush, inner=inner)
+            record(f"pofadra experts (pair by pair), {label}", ms, expert_bytes, tokens * top * 6 * w * ff)
+        # ---- the transformer's like kernels
+        hq, hk, hd = t["heads"], t["kv_heads"], t["head_dim"]
+        kvt = F.PagedKV(torch.randn(n_seqs * pages_each, hk, 64, hd, device=dev).bfloat16() * 0.1,
+                        torch.randn(n_seqs * pages_each, hk, 64, hd, device=dev).bfloat16() * 0.1, table, F.DecodeWork(dev))
+        qt = torch.randn(tokens, hq, hd, device=dev).bfloat16()
+        if n_seqs == 1:
+            ms = _event_ms(lambda: F.attention_prefill(qt, kvt, cu_q, kv_len, slots, each, hd ** -0.5, 0), flush=flush, inner=inner)
+            record(f"transformer attention, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * length * hk * hd), 4 * hq * hd * tokens * tokens / 2)
+            ms = _event_ms(lambda: F.attention_prefill(qt, kvt, cu_q, kv_len, slots, each, hd ** -0.5, window, tensor_cores="mma"), flush=flush, inner=inner)
+            record(f"transformer attention on the warp-level kernel with the same window, {label}", ms,
+                   2 * (2 * tokens * hq * hd + 2 * length * hk * hd), 4 * hq * hd * seen)
+        else:
+            sp = F.decode_splits(n_seqs, hk, length, 64, F.sm_count(dev), F.decode_cluster_places(hd, F.sm_count(dev)))
+            ms = _event_ms(lambda: F.attention_decode(qt, kvt, kv_len, slots, hd ** -0.5, 0, sp), flush=flush, inner=inner)
+            record(f"transformer attention, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * n_seqs * length * hk * hd), 4 * hq * hd * tokens * length)
+        qkv = torch.randn(tokens, (hq + 2 * hk) * hd, device=dev).bfloat16()
+        anglet = torch.arange(length, dtype=torch.float32, device=dev)[:, None] * torch.rand(hd // 2, device=dev)[None, :]
+        ones = torch.ones(hd, device=dev)
+        ms = _event_ms(lambda: F.qk_norm_rope_write(qkv, hq, hk, hd, ones, ones, 1e-6, anglet.cos().contiguous(), anglet.sin().contiguous(), tok_pos,
+                                                     tok_seq, slots, kvt, length - 1), flush=flush, inner=inner)
+        record(f"transformer q/k norm, rotation and cache write, {label}", ms, tokens * 2 * ((hq + 2 * hk) * hd + hq * hd + 2 * hk * hd))
+        hs = torch.randn(tokens, t["hidden"], device=dev)
+        delta = torch.randn(tokens, t["hidden"], device=dev).bfloat16()
+        wn = torch.ones(t["hidden"], device=dev)
+        ms = _event_ms(lambda: F.add_rmsnorm(hs, delta, wn, 1e-6, torch.bfloat16), flush=flush, inner=inner)
+        record(f"transformer residual add with next norm, {label}", ms, tokens * t["hidden"] * (4 + 2 + 4 + 2))
+        gu = torch.randn(tokens, 2 * t["ff"], device=dev).bfloat16()
+        ms = _event_ms(lambda: F.swiglu(gu, interleaved=True), flush=flush, inner=inner)
+        record(f"transformer SwiGLU, {label}", ms, tokens * t["ff"] * 6)
+    return out
+
+
+def run_compare_pofadra(args) -> dict:
+    import gc
+
+    import torch
+
+    from gtar_kimik3_public_b200.ops.library import require_device
+
+    require_device(torch.device("cuda:0"))
+    peak, peak_source = peaks()
+    results = {}
+    for name, (d, t) in POFADRA_SIZES.items():
+        entry = {}
+        for arch, raw, flops in (("pofadra", _pofadra_config(**d), _pofadra_prefill_flops(d, PREFILL_TOKENS)),
+                                 ("transformer", _transformer_config(**t), _transformer_prefill_flops(t, PREFILL_TOKENS))):
+            model = _device_model(raw)
+            ms = _time_prefill_ms(model, PREFILL_TOKENS)
+            decode = time_decode(model, args.batch, min(args.steps, 64), args.warmup)
+            entry[arch] = {
+                "weight_bytes_per_step": model.weight_bytes_per_step(),
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / (ms / 1e3), 1), "prefill_ms": round(ms, 3),
+                "prefill_frac_of_bf16_peak": round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                "decode_frac_of_hbm_peak": round(decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4),
+                "decode_launches_per_step": decode["launches"] // max(1, min(args.steps, 64)),
+            }
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        entry["kernels"] = _pofadra_kernel_table(d, t, peak)
+        results[name] = {"sizes": {"pofadra": d, "transformer": t}, **entry}
+    return {"compare": "pofadra beside transformer at equal width", "batch": args.batch, "prompt_tokens": PROMPT_LEN,
+            "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16", "data": "synthetic: random token ids, random weights drawn on the device",
+            "peaks": dict(peak, source=peak_source), "l2": "single kernels: a 192 MB buffer is written between the timed calls of the 2,048-token cases; the 8-token cases are 20 calls back to back from a CUDA graph",
+            "results": results}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -821,13 +1020,13 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--no-large", action="store_true", help="leave out the points at the 4B and 8B layer sizes")
-    parser.add_argument("--compare", default=None, choices=["dasusun"],
+    parser.add_argument("--compare", default=None, choices=["dasusun", "pofadra"],
                         help="instead of the default workload: this architecture beside the transformer at equal layer sizes")
     args = parser.parse_args()
     if args.compare:
         if args.warmup < 3:
             args.warmup = 3
-        print(json.dumps(run_compare(args)))
+        print(json.dumps(run_compare_pofadra(args) if args.compare == "pofadra" else run_compare(args)))
         return 0
     if args.impl == "reference":
         if args.warmup < 3:

@@ -198,6 +198,7 @@ struct Params {
     int n_q, n_kv, max_pages;
     float sl2;
     int window;
+    int sink;  // one more term in the softmax's denominator: a key of score 0 that has no value
     int* error_flag;
     int one_tile;  // tc2: a query tile a block, heaviest first (grid: kv head, sequence, tile), instead of a heavy and a light one
     int n_seqs, n_items;  // tc5: the list of tiles is n_items long: (tile counted from the end, sequence, kv head)
@@ -422,7 +423,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(const 
         if (ok && n_iter > 0) ok = mbar_wait(&sm.o_done, (n_iter - 1) & 1);
         fence_after();
         if (ok && n_iter > 0) {
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / (p.sink ? l + exp2f(-m_used) : l);
             __nv_bfloat16* orow = p.out + ((size_t)(q_begin + tok) * p.n_q + head) * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -826,7 +827,8 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc2_kernel(cons
             if (ok) ok = mbar_wait(&sm.sum_ready, u & 1);
             if (!ok) break;
             fence_after();
-            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
+            // (with a sink: its term against the reference exponent, which both halves of a row share)
+            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r] + (p.sink ? exp2f(-m_used) : 0.f));
             uint32_t packed[32];  // this thread's 64 columns of its row, then 16 columns of each row of the quad
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -1202,7 +1204,8 @@ __global__ void __launch_bounds__(THREADS2, 1) attention_prefill_tc5_kernel(cons
             if (ok) ok = mbar_wait(&sm.sum_ready, n & 1);
             if (!ok) break;
             fence_after();
-            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r]);
+            // (with a sink: its term against the reference exponent, which both halves of a row share)
+            const float inv = 1.0f / (sm.row_sum[0][r] + sm.row_sum[1][r] + (p.sink ? exp2f(-m_used) : 0.f));
             uint32_t packed[32];
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -1296,7 +1299,7 @@ static int prefill_tc_entry(const void* q, const void* k_pages, const void* v_pa
                             const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
                             int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
                             int page_size, long long n_pages, float scale, int window, int* error_flag,
-                            void* stream, long long n_tokens) {
+                            void* stream, long long n_tokens, int sink = 0) {
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill_tc: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(page_size == PAGE && head_dim == D, "attention_prefill_tc: needs page_size %d and head_dim %d", PAGE, D);
     GK_REQUIRE(n_kv <= 65535 && n_seqs <= 65535 && window >= 0 && max_q_len >= 0 && n_pages > 0, "attention_prefill_tc: bad sizes");
@@ -1328,6 +1331,7 @@ static int prefill_tc_entry(const void* q, const void* k_pages, const void* v_pa
     p.max_pages = max_pages;
     p.sl2 = scale * 1.4426950408889634f;
     p.window = window;
+    p.sink = sink;
     p.error_flag = error_flag;
     p.one_tile = 0;
     p.n_seqs = n_seqs;
@@ -1401,9 +1405,9 @@ GK_EXPORT int gk_attention_prefill_tc_tokens_bf16(const void* q, const void* k_p
                                                   const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
                                                   int n_seqs, int max_q_len, int n_q, int n_kv, int head_dim, int max_pages,
                                                   int page_size, long long n_pages, float scale, int window, int* error_flag,
-                                                  void* stream, long long n_tokens) {
+                                                  void* stream, long long n_tokens, int sink) {
     return prefill_tc_entry(q, k_pages, v_pages, out, cu_q, kv_len, slots, block_table, n_seqs, max_q_len, n_q, n_kv, head_dim,
-                            max_pages, page_size, n_pages, scale, window, error_flag, stream, n_tokens);
+                            max_pages, page_size, n_pages, scale, window, error_flag, stream, n_tokens, sink);
 }
 
 // With 128 keys a step: blocks that stay and take query tiles from the launch's list (where the token count is given

@@ -9,7 +9,7 @@
 // mean square, multiplied by a weight shared by the heads and by sigmoid(gate).
 //
 // Four kernels:
-//   delta_prepare   one block per token: convolutions (the inputs before the step's first token come from the
+//   delta_prepare   one block per token and head: convolutions (the inputs before the step's first token come from the
 //                   sequence's state: its last taps - 1 inputs), SiLU, unit lengths, decays and beta, all 32-bit
 //   conv_roll       moves every sequence's convolution state on by the step's inputs
 //   delta_scan      the recurrence.  A column of S (one value channel) never meets another column, so the work is
@@ -27,7 +27,7 @@
 
 namespace {
 
-constexpr int PREP_THREADS = 256;
+constexpr int PREP_THREADS = 128;
 constexpr int MAX_TAPS = 8;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
@@ -35,6 +35,22 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // proj [T, ld]: q (G d) | k (G d) | v (H dv) | b (H) | ...;  low [T, ld_low]: a (H d) | gate (H dv)
+// grid (token, unit): units 0 .. 2G-1 are the heads of q and of k (convolution, SiLU, unit length), units 2G .. 2G+H-1
+// the value heads (convolution and SiLU of the head's values, its decays and its beta).
+template <typename T>
+__device__ __forceinline__ float conv_silu(const T* __restrict__ proj, long long ld, const float* __restrict__ conv_w,
+                                           const float* __restrict__ conv_state, size_t slot, int t, int in_step, int c, int C, int taps) {
+    float y = 0.f;
+    for (int j = 0; j < taps; ++j) {  // j tokens back
+        const int at = in_step - j;
+        float x;
+        if (at >= 0) x = to_float(proj[(size_t)(t - j) * ld + c]);
+        else x = conv_state[(slot * (taps - 1) + (taps - 1 + at)) * C + c];
+        y = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], x, y);
+    }
+    return silu_f(y);
+}
+
 template <typename T, typename TL>
 __global__ void __launch_bounds__(PREP_THREADS) delta_prepare_kernel(
     const T* __restrict__ proj, long long ld, const TL* __restrict__ low, long long ld_low,
@@ -43,47 +59,39 @@ __global__ void __launch_bounds__(PREP_THREADS) delta_prepare_kernel(
     const int* __restrict__ tok_seq, const int* __restrict__ cu_q, const int* __restrict__ slots,
     float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out, float* __restrict__ g_out,
     float* __restrict__ beta_out, int n_heads, int n_kv, int d, int dv, int taps) {
-    extern __shared__ float act[];  // C floats: the activated convolution outputs of this token
+    extern __shared__ float act[];  // d floats: the activated convolution outputs of this head
+    __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, unit = blockIdx.y;
     const int seq = tok_seq[t];
     const int in_step = t - cu_q[seq];
     const size_t slot = (size_t)slots[seq];
     const int qk = n_kv * d, C = 2 * qk + n_heads * dv;
-    for (int c = threadIdx.x; c < C; c += PREP_THREADS) {
-        float y = 0.f;
-        for (int j = 0; j < taps; ++j) {  // j tokens back
-            const int at = in_step - j;
-            float x;
-            if (at >= 0) x = to_float(proj[(size_t)(t - j) * ld + c]);
-            else x = conv_state[(slot * (taps - 1) + (taps - 1 + at)) * C + c];
-            y = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], x, y);
-        }
-        act[c] = silu_f(y);
-    }
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = PREP_THREADS / 32;
-    // unit lengths: a warp per head of q and of k
-    for (int hd = warp; hd < 2 * n_kv; hd += n_warps) {
-        const float* x = act + (size_t)hd * d;
+    if (unit < 2 * n_kv) {
         float ss = 0.f;
-        for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
-        ss = warp_sum(ss);
+        for (int i = threadIdx.x; i < d; i += PREP_THREADS) {
+            const float a = conv_silu(proj, ld, conv_w, conv_state, slot, t, in_step, unit * d + i, C, taps);
+            act[i] = a;
+            ss = fmaf(a, a, ss);
+        }
+        ss = block_sum(ss, scratch);  // a fixed order for a given d: a head's length depends on the head alone
         float r = 1.f / sqrtf(ss + 1e-6f);
-        const bool is_q = hd < n_kv;
+        const bool is_q = unit < n_kv;
         if (is_q) r *= 1.f / sqrtf((float)d);
-        float* dst = (is_q ? q_out : k_out) + ((size_t)t * n_kv + (is_q ? hd : hd - n_kv)) * d;
-        for (int i = lane; i < d; i += 32) dst[i] = x[i] * r;
+        float* dst = (is_q ? q_out : k_out) + ((size_t)t * n_kv + (is_q ? unit : unit - n_kv)) * d;
+        for (int i = threadIdx.x; i < d; i += PREP_THREADS) dst[i] = act[i] * r;
+        return;
     }
-    for (int i = threadIdx.x; i < n_heads * dv; i += PREP_THREADS) v_out[(size_t)t * n_heads * dv + i] = act[2 * qk + i];
-    for (int i = threadIdx.x; i < n_heads * d; i += PREP_THREADS) {
-        const int h = i / d;
-        const float step = softplus_f(to_float(low[(size_t)t * ld_low + i]) + dt_bias[i]);
-        g_out[(size_t)t * n_heads * d + i] = expf(-expf(a_log[h]) * step);
+    const int h = unit - 2 * n_kv;
+    for (int i = threadIdx.x; i < dv; i += PREP_THREADS)
+        v_out[((size_t)t * n_heads + h) * dv + i] = conv_silu(proj, ld, conv_w, conv_state, slot, t, in_step, 2 * qk + h * dv + i, C, taps);
+    const float rate = -expf(a_log[h]);
+    for (int i = threadIdx.x; i < d; i += PREP_THREADS) {
+        const float step = softplus_f(to_float(low[(size_t)t * ld_low + (size_t)h * d + i]) + dt_bias[h * d + i]);
+        g_out[((size_t)t * n_heads + h) * d + i] = expf(rate * step);
     }
-    for (int h = threadIdx.x; h < n_heads; h += PREP_THREADS)
-        beta_out[(size_t)t * n_heads + h] = sigmoid_f(to_float(proj[(size_t)t * ld + C + h]));
+    if (threadIdx.x == 0) beta_out[(size_t)t * n_heads + h] = sigmoid_f(to_float(proj[(size_t)t * ld + C + h]));
 }
 
 // state[slot, r, c], r = 0 .. taps-2, oldest first.  After a step of n tokens row r holds the input n - (taps-1) + r of
@@ -106,12 +114,16 @@ __global__ void conv_roll_kernel(const T* __restrict__ proj, long long ld, float
 }
 
 constexpr int LPC = 8;            // lanes that share a column of the state
-constexpr int SCAN_THREADS = 256;  // 32 columns a block
+constexpr int SCAN_THREADS = 256;  // at most: 32 columns a block (the host launches 8, 16 or 32 columns a block)
 constexpr int SCAN_COLS = SCAN_THREADS / LPC;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -127,14 +139,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     const int* __restrict__ cu_q, const int* __restrict__ slots, int n_heads, int n_kv, int d, int dv) {
     constexpr int PIECE = R + 4, VEC = LPC * PIECE;
     __shared__ __align__(16) float sq[2][TB][VEC], sk[2][TB][VEC], sg[2][TB][VEC];
-    __shared__ float sv[2][TB][SCAN_COLS], sb[2][TB];
+    __shared__ __align__(16) float sv[2][TB][SCAN_COLS], sb[2][TB];
     pdl_launch_dependents();
-    const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * SCAN_COLS;
+    const int n_threads = blockDim.x, n_cols = n_threads / LPC;  // columns of this block
+    const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * n_cols;
     const int hk = head / (n_heads / n_kv);
     const int sub = threadIdx.x % LPC, col = col0 + threadIdx.x / LPC;
     const bool live = col < dv;
     // the pieces beyond d stay zero in every stage: those rows of the state never leave zero
-    for (int i = threadIdx.x; i < 2 * TB * VEC; i += SCAN_THREADS) {
+    for (int i = threadIdx.x; i < 2 * TB * VEC; i += n_threads) {
         (&sq[0][0][0])[i] = 0.f;
         (&sk[0][0][0])[i] = 0.f;
         (&sg[0][0][0])[i] = 0.f;
@@ -152,7 +165,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     const int quads = d / 4;  // 16-byte pieces of a vector of this head
     auto stage = [&](int buf, int first) {
         const int count = min(TB, n - first);
-        for (int i = threadIdx.x; i < count * quads; i += SCAN_THREADS) {
+        for (int i = threadIdx.x; i < count * quads; i += n_threads) {
             const int tt = i / quads, c4 = (i - tt * quads) * 4;
             const int lane_of = c4 / R, within = c4 - lane_of * R;
             const int at = lane_of * PIECE + within;
@@ -161,11 +174,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
             cp_async16(&sk[buf][tt][at], k + (tok * n_kv + hk) * d + c4);
             cp_async16(&sg[buf][tt][at], g + (tok * n_heads + head) * d + c4);
         }
-        for (int i = threadIdx.x; i < count * SCAN_COLS; i += SCAN_THREADS) {
-            const int tt = i / SCAN_COLS, cc = i - tt * SCAN_COLS;
-            sv[buf][tt][cc] = col0 + cc < dv ? v[((size_t)(t0 + first + tt) * n_heads + head) * dv + col0 + cc] : 0.f;
+        for (int i = threadIdx.x; i < count * n_cols; i += n_threads) {
+            const int tt = i / n_cols, cc = i - tt * n_cols;
+            if (col0 + cc < dv) cp_async4(&sv[buf][tt][cc], v + ((size_t)(t0 + first + tt) * n_heads + head) * dv + col0 + cc);
         }
-        if (threadIdx.x < count) sb[buf][threadIdx.x] = beta[(size_t)(t0 + first + threadIdx.x) * n_heads + head];
+        if (threadIdx.x < count) cp_async4(&sb[buf][threadIdx.x], beta + (size_t)(t0 + first + threadIdx.x) * n_heads + head);
         cp_async_commit();
     };
     stage(0, 0);
@@ -184,7 +197,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
             const float4* pk = reinterpret_cast<const float4*>(&sk[buf][tt][sub * PIECE]);
             const float4* pg = reinterpret_cast<const float4*>(&sg[buf][tt][sub * PIECE]);
             float kk[R], qq[R];
-            float a = 0.f, b = 0.f, c = 0.f;
+            // four partial sums each (one per place in a group of four rows): chains of R / 4 dependent operations
+            float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f}, c4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r4 = 0; r4 < R / 4; ++r4) {
                 const float4 g4 = pg[r4], k4 = pk[r4], q4 = pq[r4];
@@ -195,11 +209,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
                 for (int e = 0; e < 4; ++e) {
                     const int r = 4 * r4 + e;
                     S[r] *= gs[e];
-                    a = fmaf(S[r], kk[r], a);
-                    b = fmaf(S[r], qq[r], b);
-                    c = fmaf(kk[r], qq[r], c);
+                    a4[e] = fmaf(S[r], kk[r], a4[e]);
+                    b4[e] = fmaf(S[r], qq[r], b4[e]);
+                    c4[e] = fmaf(kk[r], qq[r], c4[e]);
                 }
             }
+            float a = (a4[0] + a4[1]) + (a4[2] + a4[3]), b = (b4[0] + b4[1]) + (b4[2] + b4[3]), c = (c4[0] + c4[1]) + (c4[2] + c4[3]);
 #pragma unroll
             for (int o = 1; o < LPC; o <<= 1) {
                 a += __shfl_xor_sync(0xffffffffu, a, o);
@@ -251,12 +266,12 @@ GK_EXPORT int gk_delta_prepare(const void* proj, int dtype, long long ld, const 
     GK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "delta_prepare: %d taps (1 to %d)", taps, MAX_TAPS);
     GK_REQUIRE(taps == 1 || conv_state != nullptr, "delta_prepare: a convolution of several taps needs its state");
     if (n_tokens == 0) return GK_OK;
-    const size_t smem = (size_t)(2 * n_kv * d + n_heads * dv) * sizeof(float);
-    GK_REQUIRE(smem <= 48 * 1024, "delta_prepare: %zu channels are more than the kernel stages", smem / 4);
+    const size_t smem = (size_t)d * sizeof(float);
+    GK_REQUIRE(smem <= 48 * 1024 && 2 * n_kv + n_heads <= 65535, "delta_prepare: heads of %d are more than the kernel stages", d);
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(dtype, T, {
         GK_DISPATCH_DTYPE(low_dtype, TL, {
-            gk_launch(delta_prepare_kernel<T, TL>, dim3(n_tokens), dim3(PREP_THREADS), smem, s, (const T*)proj, ld, (const TL*)low,
+            gk_launch(delta_prepare_kernel<T, TL>, dim3(n_tokens, 2 * n_kv + n_heads), dim3(PREP_THREADS), smem, s, (const T*)proj, ld, (const TL*)low,
                       ld_low, conv_w, conv_state, a_log, dt_bias, tok_pos, tok_seq, cu_q, slots, q_out, k_out, v_out, g_out,
                       beta_out, n_heads, n_kv, d, dv, taps);
         })
@@ -286,7 +301,18 @@ GK_EXPORT int gk_delta_scan(const float* q, const float* k, const float* v, cons
     GK_REQUIRE(d > 0 && d % 4 == 0 && d <= 256, "delta_scan: key size %d must be a multiple of 4, at most 256", d);
     GK_REQUIRE(dv > 0 && n_seqs >= 0 && n_seqs <= 65535 && n_heads <= 65535, "delta_scan: bad sizes");
     if (n_seqs == 0) return GK_OK;
-    const dim3 grid((dv + SCAN_COLS - 1) / SCAN_COLS, n_heads, n_seqs), block(SCAN_THREADS);
+    // Few (sequence, head) pairs: fewer columns a block, so that the columns of a head spread over more SMs and a token's
+    // step is not held up by the block's other warps asking shared memory for the same vectors.
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (sms <= 0) sms = 148;
+    }
+    int cols = SCAN_COLS;
+    while (cols > 8 && (long long)n_seqs * n_heads * ((dv + cols - 1) / cols) < 2LL * sms) cols /= 2;
+    const dim3 grid((dv + cols - 1) / cols, n_heads, n_seqs), block(cols * LPC);
     cudaStream_t s = (cudaStream_t)stream;
 #define GK_SCAN(R, TB)                                                                                                   \
     gk_launch(delta_scan_kernel<R, TB>, grid, block, 0, s, q, k, v, g, beta, state, out, cu_q, slots, n_heads, n_kv, d, dv)

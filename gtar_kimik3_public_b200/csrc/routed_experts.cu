@@ -1,9 +1,10 @@
 // A feed-forward of many small gated experts of which every token uses a few.
 //
-//   route        z = W_r h in 32-bit, s = sigmoid(z), choice = s + correction.  The experts form equal groups of
-//                neighbours; a group's score is the sum of its two largest choice scores and only the experts of the best
-//                `keep` groups may be chosen.  The `top` largest choice scores among them are chosen (ties: the lower
-//                index); a chosen expert's weight is its s (without the correction) times a constant.  One warp per token.
+//   route        z = W_r h in 32-bit (a warp per token and eight experts), then, a warp per token: s = sigmoid(z),
+//                choice = s + correction.  The experts form equal groups of neighbours; a group's score is the sum of its
+//                two largest choice scores and only the experts of the best `keep` groups may be chosen.  The `top`
+//                largest choice scores among them are chosen (ties: the lower index); a chosen expert's weight is its s
+//                (without the correction) times a constant.
 //   experts_up   act[pair] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair (token, chosen expert)
 //   experts_down out_t = add_t + sum over the token's pairs, in the order they were chosen, of weight * W_down[e] act[pair]
 //                (32-bit result: it is what goes into the residual stream)
@@ -11,19 +12,61 @@
 // The two expert kernels take a pair at a time, one warp per output row: the path of single-token steps, of 32-bit
 // runs and of sizes the tensor-core path does not take.  A token's result depends on the token alone.
 //
-//   sort         pairs ordered by expert for the tensor-core path: counts, starts (padded to a multiple of the tile rows),
-//                and the list of pairs of each expert
+//   sort, gather_rows, combine   many-token steps: the pairs put in the order of their experts, the tokens' rows copied
+//                into that order (each expert's rows then go through one tensor-core product, made by the caller), and
+//                the weighted sum of a token's expert outputs in the order the experts were chosen
 
 #include "common.cuh"
 
 namespace {
 
 constexpr int ROUTE_WARPS = 4;
+constexpr int SCORE_EXPERTS = 8;  // experts a warp scores at once: eight independent sums over one pass of the token's row
 
+constexpr int SCORE_TOKENS = 4;   // tokens a warp scores at once: a router row is fetched once for all of them
+
+// z[t, e] = h_t . w_router[e] in 32-bit.  One warp per (four tokens, eight experts); a lane sums its elements of a row
+// in index order and the lanes meet in the fixed order of warp_sum, so a score depends on the token's row alone.
 template <typename T>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(
-    const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction, int* __restrict__ ids,
-    float* __restrict__ weights, int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale) {
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_scores_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
+                                                                        float* __restrict__ z, int n_tokens, int width, int n_experts) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int parts = (n_experts + SCORE_EXPERTS - 1) / SCORE_EXPERTS;
+    const int token_groups = (n_tokens + SCORE_TOKENS - 1) / SCORE_TOKENS;
+    const long long unit = (long long)blockIdx.x * ROUTE_WARPS + warp;
+    if (unit >= (long long)token_groups * parts) return;
+    const int t0 = (int)(unit / parts) * SCORE_TOKENS, e0 = (int)(unit % parts) * SCORE_EXPERTS;
+    float acc[SCORE_TOKENS][SCORE_EXPERTS];
+#pragma unroll
+    for (int a = 0; a < SCORE_TOKENS; ++a)
+#pragma unroll
+        for (int j = 0; j < SCORE_EXPERTS; ++j) acc[a][j] = 0.f;
+    for (int i = lane; i < width; i += 32) {
+        float xv[SCORE_TOKENS], wv[SCORE_EXPERTS];
+#pragma unroll
+        for (int a = 0; a < SCORE_TOKENS; ++a) xv[a] = t0 + a < n_tokens ? to_float(h[(size_t)(t0 + a) * width + i]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < SCORE_EXPERTS; ++j) wv[j] = e0 + j < n_experts ? w_router[(size_t)(e0 + j) * width + i] : 0.f;
+#pragma unroll
+        for (int a = 0; a < SCORE_TOKENS; ++a)
+#pragma unroll
+            for (int j = 0; j < SCORE_EXPERTS; ++j) acc[a][j] = fmaf(xv[a], wv[j], acc[a][j]);
+    }
+#pragma unroll
+    for (int a = 0; a < SCORE_TOKENS; ++a)
+#pragma unroll
+        for (int j = 0; j < SCORE_EXPERTS; ++j) {
+            const float sum = warp_sum(acc[a][j]);
+            if (lane == 0 && t0 + a < n_tokens && e0 + j < n_experts) z[(size_t)(t0 + a) * n_experts + e0 + j] = sum;
+        }
+}
+
+// The choice from the scores: one warp per token.
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_choose_kernel(
+    const float* __restrict__ z, const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ weights,
+    int n_tokens, int n_experts, int top, int n_groups, int keep, float scale) {
     extern __shared__ float route_smem[];  // per warp: s [E] | choice [E] | group score [n_groups]
     pdl_launch_dependents();
     pdl_wait();
@@ -33,17 +76,10 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(
     float* s = route_smem + (size_t)warp * (2 * n_experts + n_groups);
     float* choice = s + n_experts;
     float* group_score = choice + n_experts;
-    const T* x = h + (size_t)t * width;
-    for (int e = 0; e < n_experts; ++e) {
-        const float* w = w_router + (size_t)e * width;
-        float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(to_float(x[i]), w[i], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float sg = 1.f / (1.f + expf(-acc));
-            s[e] = sg;
-            choice[e] = sg + correction[e];
-        }
+    for (int e = lane; e < n_experts; e += 32) {
+        const float sg = 1.f / (1.f + expf(-z[(size_t)t * n_experts + e]));
+        s[e] = sg;
+        choice[e] = sg + correction[e];
     }
     __syncwarp();
     const int per = n_experts / n_groups;
@@ -58,15 +94,13 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(
             group_score[gidx] = per > 1 ? first + second : first;
         }
         __syncwarp();
-        if (lane == 0) {
-            // the groups that are not among the best `keep` lose their experts
-            for (int gidx = 0; gidx < n_groups; ++gidx) {
-                int better = 0;
-                for (int o = 0; o < n_groups; ++o)
-                    better += (group_score[o] > group_score[gidx]) || (group_score[o] == group_score[gidx] && o < gidx);
-                if (better >= keep)
-                    for (int e = gidx * per; e < (gidx + 1) * per; ++e) choice[e] = -INFINITY;
-            }
+        // the groups that are not among the best `keep` lose their experts
+        for (int gidx = lane; gidx < n_groups; gidx += 32) {
+            int better = 0;
+            for (int o = 0; o < n_groups; ++o)
+                better += (group_score[o] > group_score[gidx]) || (group_score[o] == group_score[gidx] && o < gidx);
+            if (better >= keep)
+                for (int e = gidx * per; e < (gidx + 1) * per; ++e) choice[e] = -INFINITY;
         }
         __syncwarp();
     }
@@ -179,10 +213,105 @@ __global__ void __launch_bounds__(UP_WARPS * 32) experts_down_kernel(
     }
 }
 
+// ---- pairs in the order of their experts, for products that take all rows of an expert at once
+// One block.  ends[e] = one past the last place of expert e (cumulative counts); place_of[pair] = the pair's place in
+// that order; pair_at[place] = the pair that stands there.  Which of an expert's pairs gets which of its places is
+// settled by atomic counters and may differ from run to run; a row's product does not depend on its place.
+constexpr int SORT_THREADS = 1024;
+
+__global__ void __launch_bounds__(SORT_THREADS) experts_sort_kernel(const int* __restrict__ ids, int n_pairs, int n_experts,
+                                                                    int* __restrict__ ends, int* __restrict__ place_of,
+                                                                    int* __restrict__ pair_at) {
+    extern __shared__ int sort_smem[];  // counts [E] | starts [E]
+    pdl_launch_dependents();
+    int* counts = sort_smem;
+    int* starts = sort_smem + n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += SORT_THREADS) counts[e] = 0;
+    __syncthreads();
+    pdl_wait();
+    for (int i = threadIdx.x; i < n_pairs; i += SORT_THREADS) atomicAdd(&counts[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            starts[e] = at;
+            at += counts[e];
+            ends[e] = at;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += SORT_THREADS) {
+        const int place = atomicAdd(&starts[ids[i]], 1);
+        place_of[i] = place;
+        pair_at[place] = i;
+    }
+}
+
+// out[place] = x[pair_at[place] / top]: the rows of the tokens in the order of their experts
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ pair_at, T* __restrict__ out, int width, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t place = blockIdx.x;
+    const T* src = x + (size_t)(pair_at[place] / top) * width;
+    T* dst = out + place * width;
+    if ((width * sizeof(T)) % 16 == 0) {
+        const int n16 = width * (int)sizeof(T) / 16;
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// out_t = add_t + sum_k weights[t, k] * y[place_of[t, k]] in the order the experts were chosen (32-bit)
+template <typename T>
+__global__ void experts_combine_kernel(const T* __restrict__ y, const int* __restrict__ place_of, const float* __restrict__ weights,
+                                       const T* __restrict__ add, float* __restrict__ out, int width, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = add != nullptr ? to_float(add[t * width + c]) : 0.f;
+        for (int kk = 0; kk < top; ++kk)
+            acc = fmaf(weights[t * top + kk], to_float(y[(size_t)place_of[t * top + kk] * width + c]), acc);
+        out[t * width + c] = acc;
+    }
+}
+
 }  // namespace
 
-GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, const float* correction, int* ids, float* weights,
-                              int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale, void* stream) {
+GK_EXPORT int gk_experts_sort(const int* ids, int n_pairs, int n_experts, int* ends, int* place_of, int* pair_at, void* stream) {
+    GK_REQUIRE(n_pairs >= 0 && n_experts > 0 && n_experts <= 4096, "experts_sort: bad sizes");
+    gk_launch(experts_sort_kernel, dim3(1), dim3(SORT_THREADS), (size_t)2 * n_experts * sizeof(int), (cudaStream_t)stream, ids, n_pairs,
+              n_experts, ends, place_of, pair_at);
+    GK_CHECK_LAUNCH("experts_sort");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_gather_rows(const void* x, int dtype, const int* pair_at, void* out, int n_places, int width, int top, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && width > 0 && top > 0, "gather_rows: bad arguments");
+    if (n_places == 0) return GK_OK;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        gk_launch(gather_rows_kernel<T>, dim3(n_places), dim3(128), 0, (cudaStream_t)stream, (const T*)x, pair_at, (T*)out, width, top);
+    })
+    GK_CHECK_LAUNCH("gather_rows");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_experts_combine(const void* y, int dtype, const int* place_of, const float* weights, const void* add, float* out,
+                                 int n_tokens, int width, int top, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && width > 0 && top > 0, "experts_combine: bad arguments");
+    if (n_tokens == 0) return GK_OK;
+    GK_DISPATCH_DTYPE(dtype, T, {
+        gk_launch(experts_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, (const T*)y, place_of, weights,
+                  (const T*)add, out, width, top);
+    })
+    GK_CHECK_LAUNCH("experts_combine");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, const float* correction, float* z, int* ids,
+                              float* weights, int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype), "route_groups: bad dtype %d", dtype);
     GK_REQUIRE(n_experts > 0 && top > 0 && top <= n_experts, "route_groups: %d of %d experts", top, n_experts);
     GK_REQUIRE(n_groups >= 1 && n_experts % n_groups == 0 && keep >= 1 && keep <= n_groups, "route_groups: %d groups, %d kept, %d experts",
@@ -193,10 +322,15 @@ GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, c
     const size_t smem = (size_t)ROUTE_WARPS * (2 * n_experts + n_groups) * sizeof(float);
     GK_REQUIRE(smem <= 48 * 1024, "route_groups: too many experts (%d)", n_experts);
     cudaStream_t s = (cudaStream_t)stream;
+    const long long units = (long long)((n_tokens + SCORE_TOKENS - 1) / SCORE_TOKENS) * ((n_experts + SCORE_EXPERTS - 1) / SCORE_EXPERTS);
+    GK_REQUIRE(units / ROUTE_WARPS < 2147483647LL, "route_groups: too many tokens");
     GK_DISPATCH_DTYPE(dtype, T, {
-        gk_launch(route_kernel<T>, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, s, (const T*)h,
-                  w_router, correction, ids, weights, n_tokens, width, n_experts, top, n_groups, keep, scale);
+        gk_launch(route_scores_kernel<T>, dim3((unsigned)((units + ROUTE_WARPS - 1) / ROUTE_WARPS)), dim3(ROUTE_WARPS * 32), 0, s,
+                  (const T*)h, w_router, z, n_tokens, width, n_experts);
     })
+    GK_CHECK_LAUNCH("route_scores");
+    gk_launch(route_choose_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, s, (const float*)z,
+              correction, ids, weights, n_tokens, n_experts, top, n_groups, keep, scale);
     GK_CHECK_LAUNCH("route_groups");
     return GK_OK;
 }

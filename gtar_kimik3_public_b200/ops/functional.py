@@ -842,7 +842,7 @@ def attention_prefill(
     ``n_seqs`` sequences over the pages.  Sequence ``i`` owns tokens ``cu_q[i] .. cu_q[i+1]-1``, which
     are its last positions: ``kv_len[i]`` counts its cached tokens including them.  ``tensor_cores``:
     ``"tcgen05"`` (head size 128 only), ``"mma"`` (the warp-level kernel), or ``"auto"``.  ``sink``: one more term in
-    the softmax's denominator, a key of score 0 without a value (the warp-level kernel has it)."""
+    the softmax's denominator, a key of score 0 without a value."""
     require_device(q.device)
     _check(q, "q", torch.bfloat16, 3)
     n, n_q, d = q.shape
@@ -862,13 +862,11 @@ def attention_prefill(
         raise KernelError(f"tensor_cores must be auto, tcgen05 or mma, got {tensor_cores!r}")
     if tensor_cores == "tcgen05" and d != 128:
         raise KernelError("the tcgen05 prefill attention takes head size 128 only")
-    if sink and tensor_cores == "tcgen05":
-        raise KernelError("the tcgen05 prefill attention has no sink")
-    if not sink and (tensor_cores == "tcgen05" or (tensor_cores == "auto" and d == 128)):
+    if tensor_cores == "tcgen05" or (tensor_cores == "auto" and d == 128):
         call(
             "gk_attention_prefill_tc_tokens_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(cu_q), ptr(kv_len), ptr(slots),
             ptr(kv.block_table), n_seqs, int(max_q_len), n_q, n_kv, d, kv.max_pages, kv.page_size, kv.k.shape[0],
-            float(scale), int(window), ptr(error_flag(q.device)), stream_ptr(), int(q.shape[0]),
+            float(scale), int(window), ptr(error_flag(q.device)), stream_ptr(), int(q.shape[0]), int(sink),
         )
         return out
     call(
@@ -1349,7 +1347,8 @@ def route_groups(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tens
         raise KernelError("route_groups: router sizes do not fit")
     ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    call("gk_route_groups", ptr(h), dtype_code(h.dtype), ptr(w_router), ptr(correction), ptr(ids), ptr(weights), T, width, n_experts,
+    z = torch.empty((T, n_experts), dtype=torch.float32, device=h.device)
+    call("gk_route_groups", ptr(h), dtype_code(h.dtype), ptr(w_router), ptr(correction), ptr(z), ptr(ids), ptr(weights), T, width, n_experts,
          top, n_groups, keep, float(scale), stream_ptr())
     return ids, weights
 
@@ -1429,3 +1428,38 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     _check(x, "x", torch.float32)
     call("gk_softcap", ptr(x), x.numel(), float(cap), stream_ptr())
     return x
+
+
+def experts_sort(ids: torch.Tensor, n_experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The (token, chosen expert) pairs ``ids [T, top]`` put in the order of their experts: ``ends [E]`` (one past each
+    expert's last place), ``place_of [T, top]`` and ``pair_at [T * top]``, all int32."""
+    _check(ids, "ids", torch.int32, 2)
+    n = ids.numel()
+    ends = torch.empty((n_experts,), dtype=torch.int32, device=ids.device)
+    place_of = torch.empty_like(ids)
+    pair_at = torch.empty((n,), dtype=torch.int32, device=ids.device)
+    call("gk_experts_sort", ptr(ids), n, n_experts, ptr(ends), ptr(place_of), ptr(pair_at), stream_ptr())
+    return ends, place_of, pair_at
+
+
+def gather_rows(x: torch.Tensor, pair_at: torch.Tensor, top: int) -> torch.Tensor:
+    """``out[place] = x[pair_at[place] // top]``."""
+    _check(x, "x", dims=2)
+    _check(pair_at, "pair_at", torch.int32, 1)
+    out = torch.empty((pair_at.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    call("gk_gather_rows", ptr(x), dtype_code(x.dtype), ptr(pair_at), ptr(out), pair_at.shape[0], x.shape[1], top, stream_ptr())
+    return out
+
+
+def experts_combine(y: torch.Tensor, place_of: torch.Tensor, weights: torch.Tensor, add: torch.Tensor | None) -> torch.Tensor:
+    """``add[t] + sum_k weights[t, k] * y[place_of[t, k]]`` in the order of ``k``, 32-bit ``[T, width]``."""
+    _check(y, "y", dims=2)
+    _check(place_of, "place_of", torch.int32, 2)
+    _check(weights, "weights", torch.float32, 2)
+    T, top = place_of.shape
+    if add is not None:
+        _check(add, "add", y.dtype, 2)
+    out = torch.empty((T, y.shape[1]), dtype=torch.float32, device=y.device)
+    call("gk_experts_combine", ptr(y), dtype_code(y.dtype), ptr(place_of), ptr(weights), ptr(add), ptr(out), T, y.shape[1], top,
+         stream_ptr())
+    return out

@@ -62,7 +62,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_attention_decode_bf16_no_alloc": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_prefill_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "gk_attention_prefill_tc_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P],
-    "gk_attention_prefill_tc_tokens_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P, L],
+    "gk_attention_prefill_tc_tokens_bf16": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, F, I, P, P, L, I],
     "gk_set_attention_prefill_stay": [I],
     "gk_argmax": [P, L, I, I, P, I, P, P],
     "gk_sample": [P, L, I, I, F, I, U, P, P, I, P, I, P, P],
@@ -70,9 +70,12 @@ _SIGNATURES: dict[str, list] = {
     "gk_conv_roll": [P, I, L, P, P, P, I, I, I, P],
     "gk_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "gk_head_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, P],
-    "gk_route_groups": [P, I, P, P, P, P, I, I, I, I, I, I, F, P],
+    "gk_route_groups": [P, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
     "gk_experts_up": [P, I, P, I, P, P, I, I, I, I, P],
     "gk_experts_down": [P, I, P, I, P, P, P, P, I, I, I, I, P],
+    "gk_experts_sort": [P, I, I, P, P, P, P],
+    "gk_gather_rows": [P, I, P, P, I, I, I, P],
+    "gk_experts_combine": [P, I, P, P, P, P, I, I, I, P],
     "gk_wide_norm_rope_write": [P, I, L, P, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "gk_sigmoid_gate": [P, P, L, P, I, L, I, P],
     "gk_softcap": [P, L, F, P],

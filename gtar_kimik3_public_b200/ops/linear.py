@@ -92,3 +92,19 @@ def linear_normed(h: torch.Tensor, norm_weight: torch.Tensor, eps: float, weight
 def linear_residual(x: torch.Tensor, weight: torch.Tensor, h: torch.Tensor) -> None:
     """``h += bfloat16(x @ weight.T)`` in the product's output stage."""
     F.gemv_stream(weight, x=x, resid=h)
+
+
+def grouped_product_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``linear_grouped`` takes these operands: bfloat16, rows of 16-byte multiples, and a library that has the
+    grouped product."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and weight.shape[1] % 8 == 0
+            and hasattr(torch, "_grouped_mm"))
+
+
+def linear_grouped(x: torch.Tensor, weight: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
+    """Rows ``ends[e-1] .. ends[e]-1`` of ``x [P, K]`` times ``weight[e] [N, K]`` transposed, for every ``e``: many-token
+    products of a routed feed-forward, with the rows already in the order of their experts.  Like the plain many-token
+    product it has nothing fused behind it and goes to the library's grouped product (32-bit accumulation, bfloat16
+    result); the group boundaries stay on the device."""
+    require_device(x.device)
+    return torch._grouped_mm(x, weight.transpose(1, 2), offs=ends, out_dtype=torch.bfloat16)

@@ -18,6 +18,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
+from ..ops.linear import grouped_product_ok, linear_grouped
 from .base import FeedForward, StepContext, TensorSpec, register_part
 
 
@@ -33,6 +34,9 @@ class RoutedExperts(FeedForward):
         if not 1 <= self.top <= self.keep * (self.n_experts // self.n_groups):
             raise ValueError(f"{self.top} experts cannot be chosen from {self.keep} groups of {self.n_experts // self.n_groups}")
         self.w_gate_up = self.w_down = self.w_router = self.correction = None
+        # from this many (token, expert) pairs on, a bfloat16 step sorts its pairs by expert and runs each expert's rows
+        # through one tensor-core product; below, every pair streams its expert's weights by itself
+        self.grouped_from_pairs = 256
 
     def tensor_specs(self):
         W, ff = self.hidden_size, self.ff
@@ -65,6 +69,12 @@ class RoutedExperts(FeedForward):
     def forward_added(self, x: torch.Tensor, ctx: StepContext, add: torch.Tensor | None) -> torch.Tensor:
         """``add + experts(x)`` as one 32-bit sum (``add``: another branch's output for the same tokens, or None)."""
         ids, weights = self.route(x)
+        if x.shape[0] * self.top >= self.grouped_from_pairs and self.ff % 8 == 0 and grouped_product_ok(x, self.w_down):
+            # many tokens: the pairs in the order of their experts, each expert's rows through one product
+            ends, place_of, pair_at = F.experts_sort(ids, self.n_experts)
+            rows = F.gather_rows(x, pair_at, self.top)
+            act = F.swiglu(linear_grouped(rows, self.w_gate_up.view(self.n_experts, 2 * self.ff, self.hidden_size), ends))
+            return F.experts_combine(linear_grouped(act, self.w_down, ends), place_of, weights, add)
         return F.experts_pairwise(x, self.w_gate_up, self.w_down, ids, weights, add)
 
     def forward(self, x, ctx: StepContext) -> torch.Tensor:

@@ -264,11 +264,12 @@ def _attend(kind, q, kv, positions, seqs, slots, lens, scale, window):
     for s in sorted(set(seqs)):
         starts.append(starts[-1] + seqs.count(s))
     return F().attention_prefill(q, kv, i32(starts), i32(lens), slots, max(b - a for a, b in zip(starts, starts[1:])), scale, window,
-                                 tensor_cores="mma", sink=True)
+                                 tensor_cores="tcgen05" if kind == "prefill_tc" else "mma", sink=True)
 
 
 @pytest.mark.parametrize("kind,dtype,d", [("exact", torch.float32, 24), ("exact", torch.bfloat16, 64), ("prefill", torch.bfloat16, 64),
-                                          ("prefill", torch.bfloat16, 128), ("decode", torch.bfloat16, 64), ("decode", torch.bfloat16, 128)])
+                                          ("prefill", torch.bfloat16, 128), ("prefill_tc", torch.bfloat16, 128), ("decode", torch.bfloat16, 64),
+                                          ("decode", torch.bfloat16, 128)])
 def test_attention_with_a_sink_random(kind, dtype, d):
     n_q, n_kv, window, scale = 4, 2, 100, 0.11
     lens = [300, 77]
@@ -277,7 +278,7 @@ def test_attention_with_a_sink_random(kind, dtype, d):
     vs = [rand(n, n_kv, d, seed=30 + i).to(dtype) for i, n in enumerate(lens)]
     for i in range(2):
         fill_pages(kv, table, int(slots[i]), ks[i], vs[i])
-    new = [1, 1] if kind == "decode" else [120, 77]
+    new = [1, 1] if kind == "decode" else [220, 77]
     qs = [rand(m, n_q, d, seed=40 + i).to(dtype) for i, m in enumerate(new)]
     positions = [p for i in range(2) for p in range(lens[i] - new[i], lens[i])]
     seqs = [i for i in range(2) for _ in range(new[i])]
@@ -292,7 +293,7 @@ def test_attention_with_a_sink_random(kind, dtype, d):
 
 
 @pytest.mark.parametrize("kind,dtype,d", [("exact", torch.float32, 32), ("prefill", torch.bfloat16, 64), ("decode", torch.bfloat16, 64),
-                                          ("prefill", torch.bfloat16, 128), ("decode", torch.bfloat16, 128)])
+                                          ("prefill", torch.bfloat16, 128), ("prefill_tc", torch.bfloat16, 128), ("decode", torch.bfloat16, 128)])
 def test_attention_sink_weight_and_window_edges(kind, dtype, d):
     """One key stands out (score 12.5 against about 0 elsewhere): at the window's last place inside it carries the
     output; a key just outside with a far larger score must not be seen; where every score is strongly negative the
