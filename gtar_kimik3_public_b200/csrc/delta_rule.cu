@@ -9,9 +9,10 @@
 // mean square, multiplied by a weight shared by the heads and by sigmoid(gate).
 //
 // Four kernels:
-//   delta_prepare   one block per token and head: convolutions (the inputs before the step's first token come from the
+//   delta_prepare   one warp per token and head: convolutions (the inputs before the step's first token come from the
 //                   sequence's state: its last taps - 1 inputs), SiLU, unit lengths, decays and beta, all 32-bit
-//   conv_roll       moves every sequence's convolution state on by the step's inputs
+//   conv_roll       moves every sequence's convolution state on by the step's inputs (steps of one token a sequence: the
+//                   prepare kernel does it itself)
 //   delta_scan      the recurrence.  A column of S (one value channel) never meets another column, so the work is
 //                   cut by (sequence, head, group of columns); a column's d entries are spread over eight adjacent
 //                   lanes.  Tokens are staged in shared memory some at a time.  With a = (gS)^T k, b = (gS)^T q and
@@ -35,11 +36,13 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // proj [T, ld]: q (G d) | k (G d) | v (H dv) | b (H) | ...;  low [T, ld_low]: a (H d) | gate (H dv)
-// grid (token, unit): units 0 .. 2G-1 are the heads of q and of k (convolution, SiLU, unit length), units 2G .. 2G+H-1
+// A warp per (token, unit): units 0 .. 2G-1 are the heads of q and of k (convolution, SiLU, unit length), units 2G .. 2G+H-1
 // the value heads (convolution and SiLU of the head's values, its decays and its beta).
+// `roll`: the step brings this sequence one token, and the thread moves the channel's state on itself (row r takes row
+// r + 1, the last row the token's input); only this thread touches the channel, so nothing else can read a row too late.
 template <typename T>
 __device__ __forceinline__ float conv_silu(const T* __restrict__ proj, long long ld, const float* __restrict__ conv_w,
-                                           const float* __restrict__ conv_state, size_t slot, int t, int in_step, int c, int C, int taps) {
+                                           float* conv_state, size_t slot, int t, int in_step, int c, int C, int taps, bool roll) {
     float y = 0.f;
     for (int j = 0; j < taps; ++j) {  // j tokens back
         const int at = in_step - j;
@@ -48,50 +51,63 @@ __device__ __forceinline__ float conv_silu(const T* __restrict__ proj, long long
         else x = conv_state[(slot * (taps - 1) + (taps - 1 + at)) * C + c];
         y = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], x, y);
     }
+    if (roll && taps > 1) {
+        float* mine = conv_state + slot * (taps - 1) * C + c;
+        for (int r = 0; r + 1 < taps - 1; ++r) mine[(size_t)r * C] = mine[(size_t)(r + 1) * C];
+        mine[(size_t)(taps - 2) * C] = to_float(proj[(size_t)t * ld + c]);
+    }
     return silu_f(y);
 }
+
+constexpr int PREP_PER_LANE = 8;  // a head's channels a lane holds: heads of up to 256
 
 template <typename T, typename TL>
 __global__ void __launch_bounds__(PREP_THREADS) delta_prepare_kernel(
     const T* __restrict__ proj, long long ld, const TL* __restrict__ low, long long ld_low,
-    const float* __restrict__ conv_w /* [C, taps] */, const float* __restrict__ conv_state /* [slots, taps-1, C] */,
+    const float* __restrict__ conv_w /* [C, taps] */, float* conv_state /* [slots, taps-1, C] */,
     const float* __restrict__ a_log, const float* __restrict__ dt_bias, const int* __restrict__ tok_pos,
     const int* __restrict__ tok_seq, const int* __restrict__ cu_q, const int* __restrict__ slots,
     float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out, float* __restrict__ g_out,
-    float* __restrict__ beta_out, int n_heads, int n_kv, int d, int dv, int taps) {
-    extern __shared__ float act[];  // d floats: the activated convolution outputs of this head
-    __shared__ float scratch[33];
+    float* __restrict__ beta_out, int n_tokens, int n_heads, int n_kv, int d, int dv, int taps, int roll_single) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, unit = blockIdx.y;
+    // a warp per (token, unit); a lane's sums run in index order and the lanes meet in warp_sum's fixed order
+    const int lane = threadIdx.x & 31, units = 2 * n_kv + n_heads;
+    const long long item = (long long)blockIdx.x * (PREP_THREADS / 32) + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * units) return;
+    const int t = (int)(item / units), unit = (int)(item - (long long)t * units);
     const int seq = tok_seq[t];
     const int in_step = t - cu_q[seq];
     const size_t slot = (size_t)slots[seq];
     const int qk = n_kv * d, C = 2 * qk + n_heads * dv;
     if (unit < 2 * n_kv) {
+        float act[PREP_PER_LANE];
         float ss = 0.f;
-        for (int i = threadIdx.x; i < d; i += PREP_THREADS) {
-            const float a = conv_silu(proj, ld, conv_w, conv_state, slot, t, in_step, unit * d + i, C, taps);
-            act[i] = a;
-            ss = fmaf(a, a, ss);
+#pragma unroll
+        for (int e = 0; e < PREP_PER_LANE; ++e) {
+            const int i = lane + 32 * e;
+            act[e] = i < d ? conv_silu(proj, ld, conv_w, conv_state, slot, t, in_step, unit * d + i, C, taps, roll_single != 0) : 0.f;
+            ss = fmaf(act[e], act[e], ss);
         }
-        ss = block_sum(ss, scratch);  // a fixed order for a given d: a head's length depends on the head alone
+        ss = warp_sum(ss);
         float r = 1.f / sqrtf(ss + 1e-6f);
         const bool is_q = unit < n_kv;
         if (is_q) r *= 1.f / sqrtf((float)d);
         float* dst = (is_q ? q_out : k_out) + ((size_t)t * n_kv + (is_q ? unit : unit - n_kv)) * d;
-        for (int i = threadIdx.x; i < d; i += PREP_THREADS) dst[i] = act[i] * r;
+#pragma unroll
+        for (int e = 0; e < PREP_PER_LANE; ++e)
+            if (lane + 32 * e < d) dst[lane + 32 * e] = act[e] * r;
         return;
     }
     const int h = unit - 2 * n_kv;
-    for (int i = threadIdx.x; i < dv; i += PREP_THREADS)
-        v_out[((size_t)t * n_heads + h) * dv + i] = conv_silu(proj, ld, conv_w, conv_state, slot, t, in_step, 2 * qk + h * dv + i, C, taps);
+    for (int i = lane; i < dv; i += 32)
+        v_out[((size_t)t * n_heads + h) * dv + i] = conv_silu(proj, ld, conv_w, conv_state, slot, t, in_step, 2 * qk + h * dv + i, C, taps, roll_single != 0);
     const float rate = -expf(a_log[h]);
-    for (int i = threadIdx.x; i < d; i += PREP_THREADS) {
+    for (int i = lane; i < d; i += 32) {
         const float step = softplus_f(to_float(low[(size_t)t * ld_low + (size_t)h * d + i]) + dt_bias[h * d + i]);
         g_out[((size_t)t * n_heads + h) * d + i] = expf(rate * step);
     }
-    if (threadIdx.x == 0) beta_out[(size_t)t * n_heads + h] = sigmoid_f(to_float(proj[(size_t)t * ld + C + h]));
+    if (lane == 0) beta_out[(size_t)t * n_heads + h] = sigmoid_f(to_float(proj[(size_t)t * ld + C + h]));
 }
 
 // state[slot, r, c], r = 0 .. taps-2, oldest first.  After a step of n tokens row r holds the input n - (taps-1) + r of
@@ -113,9 +129,8 @@ __global__ void conv_roll_kernel(const T* __restrict__ proj, long long ld, float
     }
 }
 
-constexpr int LPC = 8;            // lanes that share a column of the state
-constexpr int SCAN_THREADS = 256;  // at most: 32 columns a block (the host launches 8, 16 or 32 columns a block)
-constexpr int SCAN_COLS = SCAN_THREADS / LPC;
+constexpr int SCAN_THREADS = 256;  // at most
+constexpr int SCAN_COLS = 32;      // at most 32 columns a block (the host launches fewer where the device would stand idle)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -129,15 +144,17 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// R: state entries a lane holds (d <= 8 R); TB: tokens staged at a time.  A lane's entries are the rows
-// lane * R .. lane * R + R - 1; in shared memory a lane's piece of a vector starts at lane * (R + 4) floats, so that
-// the eight 16-byte loads of a quarter warp fall into different banks.
-template <int R, int TB>
+// LPC: lanes that share a column of the state; R: state entries a lane holds (d <= LPC * R); TB: tokens staged at a
+// time.  A lane's entries are the rows lane * R .. lane * R + R - 1; in shared memory a lane's piece of a vector starts
+// at lane * PIECE floats, padded so that the 16-byte loads of the lanes fall into different banks.  A token's step is
+// one chain of dependent instructions of a warp (it showed as 209 instructions a token at three cycles each with eight
+// lanes a column and sixteen rows a lane): more lanes a column shorten the chain and lengthen the exchange.
+template <int R, int TB, int LPC>
 __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ g,
     const float* __restrict__ beta, float* __restrict__ state /* [slots, H, d, dv] */, float* __restrict__ out /* [T, H, dv] */,
     const int* __restrict__ cu_q, const int* __restrict__ slots, int n_heads, int n_kv, int d, int dv) {
-    constexpr int PIECE = R + 4, VEC = LPC * PIECE;
+    constexpr int PIECE = R == 4 ? 4 : R + 4, VEC = LPC * PIECE;
     __shared__ __align__(16) float sq[2][TB][VEC], sk[2][TB][VEC], sg[2][TB][VEC];
     __shared__ __align__(16) float sv[2][TB][SCAN_COLS], sb[2][TB];
     pdl_launch_dependents();
@@ -165,14 +182,27 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     const int quads = d / 4;  // 16-byte pieces of a vector of this head
     auto stage = [&](int buf, int first) {
         const int count = min(TB, n - first);
-        for (int i = threadIdx.x; i < count * quads; i += n_threads) {
-            const int tt = i / quads, c4 = (i - tt * quads) * 4;
-            const int lane_of = c4 / R, within = c4 - lane_of * R;
-            const int at = lane_of * PIECE + within;
-            const size_t tok = (size_t)(t0 + first + tt);
-            cp_async16(&sq[buf][tt][at], q + (tok * n_kv + hk) * d + c4);
-            cp_async16(&sk[buf][tt][at], k + (tok * n_kv + hk) * d + c4);
-            cp_async16(&sg[buf][tt][at], g + (tok * n_heads + head) * d + c4);
+        if (n_threads % quads == 0) {  // a thread's piece of a vector is the same for every token it copies
+            const int c4 = (threadIdx.x % quads) * 4, step = n_threads / quads;
+            const int at = (c4 / R) * PIECE + c4 % R;
+            const float* pq_ = q + ((size_t)(t0 + first) * n_kv + hk) * d + c4;
+            const float* pk_ = k + ((size_t)(t0 + first) * n_kv + hk) * d + c4;
+            const float* pg_ = g + ((size_t)(t0 + first) * n_heads + head) * d + c4;
+            for (int tt = threadIdx.x / quads; tt < count; tt += step) {
+                cp_async16(&sq[buf][tt][at], pq_ + (size_t)tt * n_kv * d);
+                cp_async16(&sk[buf][tt][at], pk_ + (size_t)tt * n_kv * d);
+                cp_async16(&sg[buf][tt][at], pg_ + (size_t)tt * n_heads * d);
+            }
+        } else {
+            for (int i = threadIdx.x; i < count * quads; i += n_threads) {
+                const int tt = i / quads, c4 = (i - tt * quads) * 4;
+                const int lane_of = c4 / R, within = c4 - lane_of * R;
+                const int at = lane_of * PIECE + within;
+                const size_t tok = (size_t)(t0 + first + tt);
+                cp_async16(&sq[buf][tt][at], q + (tok * n_kv + hk) * d + c4);
+                cp_async16(&sk[buf][tt][at], k + (tok * n_kv + hk) * d + c4);
+                cp_async16(&sg[buf][tt][at], g + (tok * n_heads + head) * d + c4);
+            }
         }
         for (int i = threadIdx.x; i < count * n_cols; i += n_threads) {
             const int tt = i / n_cols, cc = i - tt * n_cols;
@@ -192,7 +222,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
         }
         __syncthreads();
         const int count = min(TB, n - first);
-        for (int tt = 0; tt < count; ++tt) {
+        float* out_at = out + ((size_t)(t0 + first) * n_heads + head) * dv + col;
+        const float* v_at = &sv[buf][0][threadIdx.x / LPC];
+#pragma unroll 2
+        for (int tt = 0; tt < count; ++tt, out_at += (size_t)n_heads * dv, v_at += SCAN_COLS) {
             const float4* pq = reinterpret_cast<const float4*>(&sq[buf][tt][sub * PIECE]);
             const float4* pk = reinterpret_cast<const float4*>(&sk[buf][tt][sub * PIECE]);
             const float4* pg = reinterpret_cast<const float4*>(&sg[buf][tt][sub * PIECE]);
@@ -221,10 +254,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
                 b += __shfl_xor_sync(0xffffffffu, b, o);
                 c += __shfl_xor_sync(0xffffffffu, c, o);
             }
-            const float u = sb[buf][tt] * (sv[buf][tt][threadIdx.x / LPC] - a);
+            const float u = sb[buf][tt] * (*v_at - a);
 #pragma unroll
             for (int r = 0; r < R; ++r) S[r] = fmaf(kk[r], u, S[r]);
-            if (live && sub == 0) out[((size_t)(t0 + first + tt) * n_heads + head) * dv + col] = fmaf(u, c, b);
+            if (live && sub == 0) *out_at = fmaf(u, c, b);
         }
         __syncthreads();  // the stage is free for the load after next
     }
@@ -257,23 +290,25 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
 }  // namespace
 
 GK_EXPORT int gk_delta_prepare(const void* proj, int dtype, long long ld, const void* low, int low_dtype, long long ld_low,
-                               const float* conv_w, const float* conv_state, const float* a_log, const float* dt_bias,
+                               const float* conv_w, float* conv_state, const float* a_log, const float* dt_bias,
                                const int* tok_pos, const int* tok_seq, const int* cu_q, const int* slots, float* q_out,
                                float* k_out, float* v_out, float* g_out, float* beta_out, int n_tokens, int n_heads, int n_kv,
-                               int d, int dv, int taps, void* stream) {
+                               int d, int dv, int taps, int roll_single, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(low_dtype), "delta_prepare: bad dtype");
     GK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0 && d > 0 && dv > 0, "delta_prepare: bad sizes");
     GK_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "delta_prepare: %d taps (1 to %d)", taps, MAX_TAPS);
     GK_REQUIRE(taps == 1 || conv_state != nullptr, "delta_prepare: a convolution of several taps needs its state");
     if (n_tokens == 0) return GK_OK;
-    const size_t smem = (size_t)d * sizeof(float);
-    GK_REQUIRE(smem <= 48 * 1024 && 2 * n_kv + n_heads <= 65535, "delta_prepare: heads of %d are more than the kernel stages", d);
+    GK_REQUIRE(d <= 32 * PREP_PER_LANE, "delta_prepare: key heads of %d are more than a warp holds (%d)", d, 32 * PREP_PER_LANE);
+    const long long items = (long long)n_tokens * (2 * n_kv + n_heads);
+    const long long blocks = (items + PREP_THREADS / 32 - 1) / (PREP_THREADS / 32);
+    GK_REQUIRE(blocks < 2147483647LL, "delta_prepare: too many tokens");
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(dtype, T, {
         GK_DISPATCH_DTYPE(low_dtype, TL, {
-            gk_launch(delta_prepare_kernel<T, TL>, dim3(n_tokens, 2 * n_kv + n_heads), dim3(PREP_THREADS), smem, s, (const T*)proj, ld, (const TL*)low,
+            gk_launch(delta_prepare_kernel<T, TL>, dim3((unsigned)blocks), dim3(PREP_THREADS), 0, s, (const T*)proj, ld, (const TL*)low,
                       ld_low, conv_w, conv_state, a_log, dt_bias, tok_pos, tok_seq, cu_q, slots, q_out, k_out, v_out, g_out,
-                      beta_out, n_heads, n_kv, d, dv, taps);
+                      beta_out, n_tokens, n_heads, n_kv, d, dv, taps, roll_single);
         })
     })
     GK_CHECK_LAUNCH("delta_prepare");
@@ -296,7 +331,7 @@ GK_EXPORT int gk_conv_roll(const void* proj, int dtype, long long ld, float* sta
 
 GK_EXPORT int gk_delta_scan(const float* q, const float* k, const float* v, const float* g, const float* beta, float* state,
                             float* out, const int* cu_q, const int* slots, int n_seqs, int n_heads, int n_kv, int d, int dv,
-                            void* stream) {
+                            int lanes, int force_cols, void* stream) {
     GK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "delta_scan: bad head counts %d/%d", n_heads, n_kv);
     GK_REQUIRE(d > 0 && d % 4 == 0 && d <= 256, "delta_scan: key size %d must be a multiple of 4, at most 256", d);
     GK_REQUIRE(dv > 0 && n_seqs >= 0 && n_seqs <= 65535 && n_heads <= 65535, "delta_scan: bad sizes");
@@ -310,16 +345,34 @@ GK_EXPORT int gk_delta_scan(const float* q, const float* k, const float* v, cons
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         if (sms <= 0) sms = 148;
     }
-    int cols = SCAN_COLS;
-    while (cols > 8 && (long long)n_seqs * n_heads * ((dv + cols - 1) / cols) < 2LL * sms) cols /= 2;
-    const dim3 grid((dv + cols - 1) / cols, n_heads, n_seqs), block(cols * LPC);
+    // The choice goes by the key size alone (the lanes' sums meet in another order with another number of lanes, and a
+    // token's result must not depend on what else is in the step).  Measured on 2,048 tokens of one sequence, 8 / 16 / 32
+    // lanes: heads of 64: 470 / 438 / 432 us; of 128: 664 / 600 / 607 (8 heads), 688 / 713 / 813 (16 heads), and 8 lanes
+    // are the fastest with many sequences (64 single tokens: 79 / 116 / 196 us); of 256: 1,407 / 900 / 1,031.
+    if (lanes == 0) lanes = d <= 32 ? 8 : d <= 64 ? 16 : d <= 128 ? 8 : 16;
+    GK_REQUIRE(lanes == 8 || lanes == 16 || lanes == 32, "delta_scan: 8, 16 or 32 lanes a column, not %d", lanes);
+    if (d <= 32) lanes = 8;
+    else if (d <= 64 && lanes == 32) lanes = 16;
+    int cols = SCAN_THREADS / lanes;
+    while (cols > 2 && cols * lanes > 64 && (long long)n_seqs * n_heads * ((dv + cols - 1) / cols) < 2LL * sms) cols /= 2;
+    if (force_cols > 0 && force_cols * lanes <= SCAN_THREADS && force_cols <= SCAN_COLS) cols = force_cols;
+    const dim3 grid((dv + cols - 1) / cols, n_heads, n_seqs), block(cols * lanes);
     cudaStream_t s = (cudaStream_t)stream;
-#define GK_SCAN(R, TB)                                                                                                   \
-    gk_launch(delta_scan_kernel<R, TB>, grid, block, 0, s, q, k, v, g, beta, state, out, cu_q, slots, n_heads, n_kv, d, dv)
-    if (d <= 32) GK_SCAN(4, 16);
-    else if (d <= 64) GK_SCAN(8, 16);
-    else if (d <= 128) GK_SCAN(16, 8);
-    else GK_SCAN(32, 4);
+#define GK_SCAN(R, TB, L)                                                                                                \
+    gk_launch(delta_scan_kernel<R, TB, L>, grid, block, 0, s, q, k, v, g, beta, state, out, cu_q, slots, n_heads, n_kv, d, dv)
+    if (lanes == 8) {
+        if (d <= 32) GK_SCAN(4, 16, 8);
+        else if (d <= 64) GK_SCAN(8, 16, 8);
+        else if (d <= 128) GK_SCAN(16, 8, 8);
+        else GK_SCAN(32, 4, 8);
+    } else if (lanes == 16) {
+        if (d <= 64) GK_SCAN(4, 16, 16);
+        else if (d <= 128) GK_SCAN(8, 8, 16);
+        else GK_SCAN(16, 4, 16);
+    } else {
+        if (d <= 128) GK_SCAN(4, 8, 32);
+        else GK_SCAN(8, 4, 32);
+    }
 #undef GK_SCAN
     GK_CHECK_LAUNCH("delta_scan");
     return GK_OK;

@@ -21,13 +21,13 @@
 namespace {
 
 constexpr int ROUTE_WARPS = 4;
-constexpr int SCORE_EXPERTS = 8;  // experts a warp scores at once: eight independent sums over one pass of the token's row
 
 constexpr int SCORE_TOKENS = 4;   // tokens a warp scores at once: a router row is fetched once for all of them
 
-// z[t, e] = h_t . w_router[e] in 32-bit.  One warp per (four tokens, eight experts); a lane sums its elements of a row
-// in index order and the lanes meet in the fixed order of warp_sum, so a score depends on the token's row alone.
-template <typename T>
+// z[t, e] = h_t . w_router[e] in 32-bit.  One warp per (four tokens, SCORE_EXPERTS experts: eight where tokens are many,
+// two where they are few and the launch would otherwise be a handful of warps); a lane sums its elements of a row in
+// index order and the lanes meet in the fixed order of warp_sum, so a score depends on the token's row alone.
+template <typename T, int SCORE_EXPERTS>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_scores_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
                                                                         float* __restrict__ z, int n_tokens, int width, int n_experts) {
     pdl_launch_dependents();
@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_scores_kernel(const T*
     for (int a = 0; a < SCORE_TOKENS; ++a)
 #pragma unroll
         for (int j = 0; j < SCORE_EXPERTS; ++j) acc[a][j] = 0.f;
+#pragma unroll 4
     for (int i = lane; i < width; i += 32) {
         float xv[SCORE_TOKENS], wv[SCORE_EXPERTS];
 #pragma unroll
@@ -134,6 +135,7 @@ template <>
 __device__ __forceinline__ float dot_smem<float>(const float* __restrict__ x, const float* __restrict__ w, int n, int lane) {
     float acc = 0.f;
     if ((n & 3) == 0) {
+#pragma unroll 4
         for (int i = lane * 4; i < n; i += 128) {
             const float4 a = *reinterpret_cast<const float4*>(w + i);
             acc = fmaf(x[i], a.x, acc); acc = fmaf(x[i + 1], a.y, acc); acc = fmaf(x[i + 2], a.z, acc); acc = fmaf(x[i + 3], a.w, acc);
@@ -148,6 +150,7 @@ template <>
 __device__ __forceinline__ float dot_smem<__nv_bfloat16>(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w, int n, int lane) {
     float acc = 0.f;
     if ((n & 7) == 0) {
+#pragma unroll 4
         for (int i = lane * 8; i < n; i += 256) {
             const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
             const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -162,6 +165,43 @@ __device__ __forceinline__ float dot_smem<__nv_bfloat16>(const float* __restrict
         for (int i = lane; i < n; i += 32) acc = fmaf(x[i], __bfloat162float(w[i]), acc);
     }
     return warp_sum(acc);
+}
+
+// A lane's share of NR dot products of one vector in shared memory with NR rows in memory, summed in index order; the
+// rows' loads are independent, so all of them are on their way together.  The caller finishes each with warp_sum.
+template <typename TW, int NR>
+__device__ __forceinline__ void dot_parts(const float* __restrict__ x, const TW* const (&rows)[NR], int n, int lane, float (&acc)[NR]) {
+#pragma unroll
+    for (int j = 0; j < NR; ++j) acc[j] = 0.f;
+    constexpr int VEC = 16 / sizeof(TW);
+    if (n % VEC == 0) {
+#pragma unroll 2
+        for (int i = lane * VEC; i < n; i += 32 * VEC) {
+            uint4 raw[NR];
+#pragma unroll
+            for (int j = 0; j < NR; ++j) raw[j] = *reinterpret_cast<const uint4*>(rows[j] + i);
+#pragma unroll
+            for (int j = 0; j < NR; ++j) {
+                if constexpr (sizeof(TW) == 2) {
+                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 f = __bfloat1622float2(p[c]);
+                        acc[j] = fmaf(x[i + 2 * c], f.x, acc[j]);
+                        acc[j] = fmaf(x[i + 2 * c + 1], f.y, acc[j]);
+                    }
+                } else {
+                    const float* f = reinterpret_cast<const float*>(&raw[j]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[j] = fmaf(x[i + c], f[c], acc[j]);
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32)
+#pragma unroll
+            for (int j = 0; j < NR; ++j) acc[j] = fmaf(x[i], to_float(rows[j][i]), acc[j]);
+    }
 }
 
 constexpr int UP_WARPS = 8;
@@ -182,9 +222,25 @@ __global__ void __launch_bounds__(UP_WARPS * 32) experts_up_kernel(
     const TW* wg = w_gate_up + (size_t)e * 2 * ff * width;
     const TW* wu = wg + (size_t)ff * width;
     const int f0 = blockIdx.y * rows_per_block;
-    for (int f = f0 + warp; f < min(ff, f0 + rows_per_block); f += UP_WARPS) {
-        const float gate = dot_smem<TW>(xs, wg + (size_t)f * width, width, lane);
-        const float up = dot_smem<TW>(xs, wu + (size_t)f * width, width, lane);
+    const int f_end = min(ff, f0 + rows_per_block);
+    int f = f0 + warp;
+    for (; f + UP_WARPS < f_end; f += 2 * UP_WARPS) {  // two rows of gate and of up at once: four rows' loads in flight
+        const TW* const rows[4] = {wg + (size_t)f * width, wu + (size_t)f * width, wg + (size_t)(f + UP_WARPS) * width,
+                                   wu + (size_t)(f + UP_WARPS) * width};
+        float part[4];
+        dot_parts<TW, 4>(xs, rows, width, lane, part);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part[j] = warp_sum(part[j]);
+        if (lane == 0) {
+            act[(size_t)pair * ff + f] = from_float<T>(part[0] / (1.f + expf(-part[0])) * part[1]);
+            act[(size_t)pair * ff + f + UP_WARPS] = from_float<T>(part[2] / (1.f + expf(-part[2])) * part[3]);
+        }
+    }
+    for (; f < f_end; f += UP_WARPS) {
+        const TW* const rows[2] = {wg + (size_t)f * width, wu + (size_t)f * width};
+        float part[2];
+        dot_parts<TW, 2>(xs, rows, width, lane, part);
+        const float gate = warp_sum(part[0]), up = warp_sum(part[1]);
         if (lane == 0) act[(size_t)pair * ff + f] = from_float<T>(gate / (1.f + expf(-gate)) * up);
     }
 }
@@ -204,7 +260,15 @@ __global__ void __launch_bounds__(UP_WARPS * 32) experts_down_kernel(
     const int c0 = blockIdx.y * rows_per_block;
     for (int c = c0 + warp; c < min(width, c0 + rows_per_block); c += UP_WARPS) {
         float acc = add != nullptr ? to_float(add[(size_t)t * width + c]) : 0.f;
-        for (int kk = 0; kk < top; ++kk) {
+        int kk = 0;
+        for (; kk + 1 < top; kk += 2) {  // two experts' rows in flight; the sum still takes them in the order they were chosen
+            const int e0 = ids[(size_t)t * top + kk], e1 = ids[(size_t)t * top + kk + 1];
+            const float d0 = dot_smem<TW>(as + (size_t)kk * ff, w_down + ((size_t)e0 * width + c) * ff, ff, lane);
+            const float d1 = dot_smem<TW>(as + (size_t)(kk + 1) * ff, w_down + ((size_t)e1 * width + c) * ff, ff, lane);
+            acc = fmaf(weights[(size_t)t * top + kk], d0, acc);
+            acc = fmaf(weights[(size_t)t * top + kk + 1], d1, acc);
+        }
+        if (kk < top) {
             const int e = ids[(size_t)t * top + kk];
             const float d = dot_smem<TW>(as + (size_t)kk * ff, w_down + ((size_t)e * width + c) * ff, ff, lane);
             acc = fmaf(weights[(size_t)t * top + kk], d, acc);
@@ -322,11 +386,16 @@ GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, c
     const size_t smem = (size_t)ROUTE_WARPS * (2 * n_experts + n_groups) * sizeof(float);
     GK_REQUIRE(smem <= 48 * 1024, "route_groups: too many experts (%d)", n_experts);
     cudaStream_t s = (cudaStream_t)stream;
-    const long long units = (long long)((n_tokens + SCORE_TOKENS - 1) / SCORE_TOKENS) * ((n_experts + SCORE_EXPERTS - 1) / SCORE_EXPERTS);
+    const int token_groups = (n_tokens + SCORE_TOKENS - 1) / SCORE_TOKENS;
+    const int per_warp = (long long)token_groups * ((n_experts + 7) / 8) >= 512 ? 8 : 2;
+    const long long units = (long long)token_groups * ((n_experts + per_warp - 1) / per_warp);
     GK_REQUIRE(units / ROUTE_WARPS < 2147483647LL, "route_groups: too many tokens");
+    const dim3 score_grid((unsigned)((units + ROUTE_WARPS - 1) / ROUTE_WARPS));
     GK_DISPATCH_DTYPE(dtype, T, {
-        gk_launch(route_scores_kernel<T>, dim3((unsigned)((units + ROUTE_WARPS - 1) / ROUTE_WARPS)), dim3(ROUTE_WARPS * 32), 0, s,
-                  (const T*)h, w_router, z, n_tokens, width, n_experts);
+        if (per_warp == 8)
+            gk_launch(route_scores_kernel<T, 8>, score_grid, dim3(ROUTE_WARPS * 32), 0, s, (const T*)h, w_router, z, n_tokens, width, n_experts);
+        else
+            gk_launch(route_scores_kernel<T, 2>, score_grid, dim3(ROUTE_WARPS * 32), 0, s, (const T*)h, w_router, z, n_tokens, width, n_experts);
     })
     GK_CHECK_LAUNCH("route_scores");
     gk_launch(route_choose_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, s, (const float*)z,

@@ -1253,10 +1253,12 @@ def attention_latent_tiled(q_carried: torch.Tensor, q_raw: torch.Tensor, q_rot_a
 # ------------------------------------------------------------------ the delta rule as a recurrent mixer
 def delta_prepare(proj: torch.Tensor, low: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor | None, a_log: torch.Tensor,
                   dt_bias: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor, slots: torch.Tensor,
-                  n_heads: int, n_kv: int, d: int, dv: int, taps: int):
+                  n_heads: int, n_kv: int, d: int, dv: int, taps: int, roll_single: bool = False):
     """Everything between the input projections and the recurrence, in 32-bit.  ``proj [T, >= 2 n_kv d + n_heads dv + n_heads]``
     holds q | k | v | b of every token, ``low [T, >= n_heads d + n_heads dv]`` the decay's and the gate's second
     projections; ``conv_w [channels, taps]``; ``conv_state [slots, taps - 1, channels]`` the inputs before the step.
+    ``roll_single``: every sequence of the step brings ONE token and the kernel moves the convolution state on itself
+    (otherwise ``conv_roll`` follows).
     Returns q, k ``[T, n_kv, d]`` (unit length; q also times ``d ** -0.5``), v ``[T, n_heads, dv]``, the decays
     ``[T, n_heads, d]`` and beta ``[T, n_heads]``."""
     require_device(proj.device)
@@ -1285,7 +1287,7 @@ def delta_prepare(proj: torch.Tensor, low: torch.Tensor, conv_w: torch.Tensor, c
     beta = torch.empty((T, n_heads), dtype=torch.float32, device=dev)
     call("gk_delta_prepare", ptr(proj), dtype_code(proj.dtype), proj.shape[1], ptr(low), dtype_code(low.dtype), low.shape[1],
          ptr(conv_w), ptr(conv_state) if taps > 1 else None, ptr(a_log), ptr(dt_bias), ptr(tok_pos), ptr(tok_seq), ptr(cu_q),
-         ptr(slots), ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), T, n_heads, n_kv, d, dv, taps, stream_ptr())
+         ptr(slots), ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), T, n_heads, n_kv, d, dv, taps, int(roll_single and taps > 1), stream_ptr())
     return q, k, v, g, beta
 
 
@@ -1296,6 +1298,12 @@ def conv_roll(proj: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, slots
     _check(state, "state", torch.float32, 3)
     call("gk_conv_roll", ptr(proj), dtype_code(proj.dtype), proj.shape[1], ptr(state), ptr(cu_q), ptr(slots), n_seqs, channels,
          state.shape[1] + 1, stream_ptr())
+
+
+# lanes that share a column of the state in the recurrence: 0 = the kernel's own choice by the key size; 8, 16 or 32 for
+# measurements (environment variable GTAR_B200_SCAN_LANES)
+DELTA_SCAN_LANES = int(__import__("os").environ.get("GTAR_B200_SCAN_LANES", "0"))
+DELTA_SCAN_COLS = int(__import__("os").environ.get("GTAR_B200_SCAN_COLS", "0"))  # columns a block, 0 = the kernel's choice
 
 
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
@@ -1313,7 +1321,7 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tenso
         raise KernelError("delta_scan: the state or the inputs have other sizes than the heads")
     out = torch.empty((T, n_heads, dv), dtype=torch.float32, device=q.device)
     call("gk_delta_scan", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(state), ptr(out), ptr(cu_q), ptr(slots), n_seqs, n_heads,
-         n_kv, d, dv, stream_ptr())
+         n_kv, d, dv, DELTA_SCAN_LANES, DELTA_SCAN_COLS, stream_ptr())
     return out
 
 

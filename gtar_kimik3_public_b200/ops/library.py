@@ -66,9 +66,9 @@ _SIGNATURES: dict[str, list] = {
     "gk_set_attention_prefill_stay": [I],
     "gk_argmax": [P, L, I, I, P, I, P, P],
     "gk_sample": [P, L, I, I, F, I, U, P, P, I, P, I, P, P],
-    "gk_delta_prepare": [P, I, L, P, I, L, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "gk_delta_prepare": [P, I, L, P, I, L, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "gk_conv_roll": [P, I, L, P, P, P, I, I, I, P],
-    "gk_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "gk_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "gk_head_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, P],
     "gk_route_groups": [P, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
     "gk_experts_up": [P, I, P, I, P, P, I, I, I, I, P],

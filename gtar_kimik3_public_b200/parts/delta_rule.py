@@ -111,8 +111,9 @@ class ChannelDeltaRule(Mixer):
         proj = linear(x, self.w_in)
         low = linear(linear(x, self.w_low1), self.w_low2, torch.float32)
         q, k, v, g, beta = F.delta_prepare(proj, low, self.conv_w, conv_state, self.a_log, self.dt_bias, ctx.tok_pos, ctx.tok_seq,
-                                           ctx.cu_q, ctx.slots, self.n_heads, self.n_kv, self.d, self.dv, self.taps)
-        if conv_state is not None:
+                                           ctx.cu_q, ctx.slots, self.n_heads, self.n_kv, self.d, self.dv, self.taps,
+                                           roll_single=ctx.all_single)
+        if conv_state is not None and not ctx.all_single:
             F.conv_roll(proj, conv_state, ctx.cu_q, ctx.slots, ctx.n_seqs, self.channels)
         o = F.delta_scan(q, k, v, g, beta, state, ctx.cu_q, ctx.slots, ctx.n_seqs)
         y = F.head_norm_gate(o, self.norm_w, low, self.n_heads * self.d, self.norm_eps, ctx.dtype)
