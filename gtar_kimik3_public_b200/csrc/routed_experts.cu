@@ -22,12 +22,12 @@ namespace {
 
 constexpr int ROUTE_WARPS = 4;
 
-constexpr int SCORE_TOKENS = 4;   // tokens a warp scores at once: a router row is fetched once for all of them
 
-// z[t, e] = h_t . w_router[e] in 32-bit.  One warp per (four tokens, SCORE_EXPERTS experts: eight where tokens are many,
-// two where they are few and the launch would otherwise be a handful of warps); a lane sums its elements of a row in
-// index order and the lanes meet in the fixed order of warp_sum, so a score depends on the token's row alone.
-template <typename T, int SCORE_EXPERTS>
+// z[t, e] = h_t . w_router[e] in 32-bit.  One warp per (SCORE_TOKENS tokens, SCORE_EXPERTS experts): eight and eight where
+// tokens are many (a router row is fetched once for eight tokens), four and two where they are few and the launch would
+// otherwise be a handful of warps; a lane sums its elements of a row in index order and the lanes meet in the fixed order
+// of warp_sum, so a score depends on the token's row alone.
+template <typename T, int SCORE_EXPERTS, int SCORE_TOKENS>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_scores_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
                                                                         float* __restrict__ z, int n_tokens, int width, int n_experts) {
     pdl_launch_dependents();
@@ -386,16 +386,17 @@ GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, c
     const size_t smem = (size_t)ROUTE_WARPS * (2 * n_experts + n_groups) * sizeof(float);
     GK_REQUIRE(smem <= 48 * 1024, "route_groups: too many experts (%d)", n_experts);
     cudaStream_t s = (cudaStream_t)stream;
-    const int token_groups = (n_tokens + SCORE_TOKENS - 1) / SCORE_TOKENS;
-    const int per_warp = (long long)token_groups * ((n_experts + 7) / 8) >= 512 ? 8 : 2;
+    const bool many = (long long)((n_tokens + 7) / 8) * ((n_experts + 7) / 8) >= 512;
+    const int per_warp = many ? 8 : 2;
+    const int token_groups = (n_tokens + (many ? 8 : 4) - 1) / (many ? 8 : 4);
     const long long units = (long long)token_groups * ((n_experts + per_warp - 1) / per_warp);
     GK_REQUIRE(units / ROUTE_WARPS < 2147483647LL, "route_groups: too many tokens");
     const dim3 score_grid((unsigned)((units + ROUTE_WARPS - 1) / ROUTE_WARPS));
     GK_DISPATCH_DTYPE(dtype, T, {
         if (per_warp == 8)
-            gk_launch(route_scores_kernel<T, 8>, score_grid, dim3(ROUTE_WARPS * 32), 0, s, (const T*)h, w_router, z, n_tokens, width, n_experts);
+            gk_launch(route_scores_kernel<T, 8, 8>, score_grid, dim3(ROUTE_WARPS * 32), 0, s, (const T*)h, w_router, z, n_tokens, width, n_experts);
         else
-            gk_launch(route_scores_kernel<T, 2>, score_grid, dim3(ROUTE_WARPS * 32), 0, s, (const T*)h, w_router, z, n_tokens, width, n_experts);
+            gk_launch(route_scores_kernel<T, 2, 4>, score_grid, dim3(ROUTE_WARPS * 32), 0, s, (const T*)h, w_router, z, n_tokens, width, n_experts);
     })
     GK_CHECK_LAUNCH("route_scores");
     gk_launch(route_choose_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, s, (const float*)z,
