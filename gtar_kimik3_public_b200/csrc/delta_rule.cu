@@ -224,11 +224,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
         const int count = min(TB, n - first);
         float* out_at = out + ((size_t)(t0 + first) * n_heads + head) * dv + col;
         const float* v_at = &sv[buf][0][threadIdx.x / LPC];
+        const float* b_at = &sb[buf][0];
+        // every address of the loop moves on by a constant a token
+        const float4* pq = reinterpret_cast<const float4*>(&sq[buf][0][sub * PIECE]);
+        const float4* pk = reinterpret_cast<const float4*>(&sk[buf][0][sub * PIECE]);
+        const float4* pg = reinterpret_cast<const float4*>(&sg[buf][0][sub * PIECE]);
+        const size_t out_step = (size_t)n_heads * dv;
 #pragma unroll 2
-        for (int tt = 0; tt < count; ++tt, out_at += (size_t)n_heads * dv, v_at += SCAN_COLS) {
-            const float4* pq = reinterpret_cast<const float4*>(&sq[buf][tt][sub * PIECE]);
-            const float4* pk = reinterpret_cast<const float4*>(&sk[buf][tt][sub * PIECE]);
-            const float4* pg = reinterpret_cast<const float4*>(&sg[buf][tt][sub * PIECE]);
+        for (int tt = 0; tt < count; ++tt, out_at += out_step, v_at += SCAN_COLS, ++b_at, pq += VEC / 4, pk += VEC / 4, pg += VEC / 4) {
             float kk[R], qq[R];
             // four partial sums each (one per place in a group of four rows): chains of R / 4 dependent operations
             float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f}, c4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -254,7 +257,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
                 b += __shfl_xor_sync(0xffffffffu, b, o);
                 c += __shfl_xor_sync(0xffffffffu, c, o);
             }
-            const float u = sb[buf][tt] * (*v_at - a);
+            const float u = *b_at * (*v_at - a);
 #pragma unroll
             for (int r = 0; r < R; ++r) S[r] = fmaf(kk[r], u, S[r]);
             if (live && sub == 0) *out_at = fmaf(u, c, b);

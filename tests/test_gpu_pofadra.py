@@ -220,3 +220,19 @@ def test_trace_replay_from_the_command_line(tag, dtype, tmp_path):
         pof_check(tag, dtype, a, [70 + i], rows[:1], f"trace step {i + 1}, request a")
         if i < 2:
             pof_check(tag, dtype, b, [18 + i], rows[1:], f"trace step {i + 1}, request b")
+
+
+@pytest.mark.parametrize("tag,dtype", [("pof_c_all", "bfloat16"), ("pof_c", "float32"), ("pof_a", "float32")])
+def test_a_prompt_shape_seen_again_replays_from_a_graph(tag, dtype):
+    """A many-token step is captured when its shape comes a second time and replayed from then on (the experts' sorted
+    path with its group boundaries in device memory included): other prompts of the same length, in slots and states that
+    were used before, give the plain implementation's logits each time."""
+    engine = pof_engine(tag, dtype, max_tokens=256, max_seqs=2)
+    spoil(engine)
+    for r, tokens in enumerate(pof_requests(tag, [83, 83, 83, 83], seed=17)):
+        logits = engine.step([_entry(r, tokens, [0, 41, 82])])
+        engine.end([r])
+        pof_check(tag, dtype, tokens, [0, 41, 82], logits, f"{tag} {dtype} prompt {r} of one shape")
+        spoil(engine)
+    assert engine.graphs is not None and any(key[3] == 83 for key in engine.graphs.graphs)
+    engine.check()
