@@ -175,7 +175,8 @@ def test_route_groups_the_best_expert_loses_with_its_group():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,ff,E,top,n", [(72, 24, 5, 5, 7), (96, 48, 6, 2, 33), (128, 100, 8, 3, 1), (70, 30, 3, 1, 5)])
+@pytest.mark.parametrize("width,ff,E,top,n", [(72, 24, 5, 5, 7), (96, 48, 6, 2, 33), (128, 100, 8, 3, 1), (70, 30, 3, 1, 5),
+                                              (64, 2048, 9, 8, 2)])  # the last: more than 48 KB of staged activations
 def test_experts_pairwise(dtype, width, ff, E, top, n):
     h = rand(n, width, seed=1).to(dtype)
     w = {}
