@@ -824,7 +824,7 @@ def _pofadra_config(width, layers, heads, kv_heads, dim, vdim, conv, rank, a_hea
     stack = [{"type": "attention" if i % 4 == 3 else "channel_delta", "mixer": attention if i % 4 == 3 else delta, "mlp": mlp}
              for i in range(layers)]
     return {"architecture": "Pofadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
-            "logit_softcap": 30.0, "layers": stack, "initializer_range": 0.02, "max_position_embeddings": 4096}
+            "logit_softcap": 40.0, "layers": stack, "initializer_range": 0.02, "max_position_embeddings": 4096}
 
 
 POFADRA_SIZES = {

@@ -36,7 +36,7 @@ POF_A = {
         _layer("channel_delta", _delta(4, 2, 24, 40, 3, decay_rank=12, gate_rank=20), _moe(48, 6, 2, 2.5, 3, 2)),
         _layer("attention", _attention(6, 2, 16, 0.3, window=17, rot_dims=8, base=100.0), _moe(40, 4, 1, 1.0)),
         _layer("channel_delta", _delta(2, 2, 64, 16, 1), None),
-        _layer("attention", _attention(2, 2, 40, 0.2, window=70, rot_dims=40), _moe(56, 8, 3, 0.7, 2, 1)),
+        _layer("attention", _attention(2, 2, 40, 0.2, window=70, rot_dims=40), _moe(56, 10, 3, 0.7, 5, 2)),
     ],
 }
 
