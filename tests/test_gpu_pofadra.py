@@ -236,3 +236,27 @@ def test_a_prompt_shape_seen_again_replays_from_a_graph(tag, dtype):
         spoil(engine)
     assert engine.graphs is not None and any(key[3] == 83 for key in engine.graphs.graphs)
     engine.check()
+
+
+def test_command_line_generates_the_greedy_tokens():
+    """The generation command line loads the folder by its config.json and prints the plain implementation's greedy tokens."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    (prompt,) = pof_requests("pof_b", [9], seed=13)
+    run = subprocess.run(
+        [sys.executable, "-m", "gtar_kimik3_public_b200.scripts.generate", "--model", str(pof_folder("pof_b")), "--dtype", "float32",
+         "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6", "--temperature", "0"],
+        capture_output=True, text=True, cwd=root, timeout=300)
+    assert run.returncode == 0, run.stderr[-2000:]
+    produced = [int(t) for t in run.stdout.strip().splitlines()[0].split(",")]
+    assert len(produced) == 6
+    sequence = list(prompt)
+    for token in produced:
+        logits = pof_plain_logits("pof_b", sequence, "f64")[-1]
+        top = torch.topk(logits, 2).values
+        if (top[0] - top[1]).item() > 1e-3:
+            assert int(logits.argmax()) == token
+        sequence.append(token)
